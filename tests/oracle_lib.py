@@ -1,0 +1,104 @@
+"""ctypes access to the CPU oracle (oracle/liboracle_attention.so) and, where it was built, to the
+reference project's own shader sources compiled as C++ (oracle/_ref/libref_attention.so).
+
+Test infrastructure: imported by tests/, __graft_entry__.smoke() and bench.py's CPU legs only."""
+import ctypes
+import os
+import subprocess
+import numpy as np
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_ODIR = os.path.join(_ROOT, "oracle")
+_f32p = ctypes.POINTER(ctypes.c_float)
+_lib = None
+_ref = None
+
+
+def build():
+    subprocess.run(["make", "-C", _ODIR, "-s"], check=True)
+
+
+def oracle():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_ODIR, "liboracle_attention.so")
+        if not os.path.exists(path):
+            build()
+        _lib = ctypes.CDLL(path)
+        _lib.oracle_attention_fwd.argtypes = [ctypes.c_int] * 6 + [_f32p] * 5 + [ctypes.c_int] * 2
+        _lib.oracle_attention_bwd.argtypes = [ctypes.c_int] * 5 + [_f32p] * 7 + [ctypes.c_int] * 2
+        _lib.oracle_f32_to_bf16.argtypes = [_f32p, ctypes.POINTER(ctypes.c_uint16), ctypes.c_int64]
+    return _lib
+
+
+def reference():
+    """The compiled reference shaders, or None when oracle/_ref was not built."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(_ODIR, "_ref", "libref_attention.so")
+        if not os.path.exists(path):
+            return None
+        _ref = ctypes.CDLL(path)
+        _ref.ref_attention_fwd.argtypes = [ctypes.c_int] * 6 + [_f32p] * 4
+        _ref.ref_attention_bwd.argtypes = [ctypes.c_int] * 4 + [_f32p] * 7
+    return _ref
+
+
+def _p(a):
+    return a.ctypes.data_as(_f32p) if a is not None else None
+
+
+def _c(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def fwd(q, k, v, causal=True, kernel=0, want_lse=True, bh_range=None):
+    """q,k,v: [B,H,S,D] fp32.  Returns (O, LSE)."""
+    q, k, v = _c(q), _c(k), _c(v)
+    B, H, S, D = q.shape
+    o = np.zeros_like(q)
+    lse = np.zeros((B, H, S), np.float32) if want_lse else None
+    b0, b1 = bh_range if bh_range else (0, -1)
+    rc = oracle().oracle_attention_fwd(B, H, S, D, int(causal), kernel, _p(q), _p(k), _p(v), _p(o), _p(lse), b0, b1)
+    if rc != 0:
+        raise ValueError("oracle rejected the arguments")
+    return o, lse
+
+
+def bwd(q, k, v, d_o, causal=True, bh_range=None):
+    """Returns (dQ, dK, dV) following the reference's composed backward."""
+    q, k, v, d_o = _c(q), _c(k), _c(v), _c(d_o)
+    B, H, S, D = q.shape
+    dq, dk, dv = np.zeros_like(q), np.zeros_like(q), np.zeros_like(q)
+    b0, b1 = bh_range if bh_range else (0, -1)
+    rc = oracle().oracle_attention_bwd(B, H, S, D, int(causal), _p(q), _p(k), _p(v), _p(d_o), _p(dq), _p(dk), _p(dv), b0, b1)
+    if rc != 0:
+        raise ValueError("oracle rejected the arguments")
+    return dq, dk, dv
+
+
+def f32_to_bf16_bits(x):
+    x = _c(x)
+    out = np.zeros(x.shape, np.uint16)
+    oracle().oracle_f32_to_bf16(_p(x), out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16)), x.size)
+    return out
+
+
+def ref_fwd(q, k, v, causal=True, kernel=0):
+    r = reference()
+    q, k, v = _c(q), _c(k), _c(v)
+    B, H, S, D = q.shape
+    o = np.zeros_like(q)
+    rc = r.ref_attention_fwd(B, H, S, D, int(causal), kernel, _p(q), _p(k), _p(v), _p(o))
+    if rc != 0:
+        raise ValueError("shape outside what the reference shaders can run")
+    return o
+
+
+def ref_bwd(q, k, v, d_o):
+    r = reference()
+    q, k, v, d_o = _c(q), _c(k), _c(v), _c(d_o)
+    B, H, S, D = q.shape
+    dq, dk, dv = np.zeros_like(q), np.zeros_like(q), np.zeros_like(q)
+    r.ref_attention_bwd(B, H, S, D, _p(q), _p(k), _p(v), _p(d_o), _p(dq), _p(dk), _p(dv))
+    return dq, dk, dv
