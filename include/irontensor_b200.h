@@ -1,0 +1,138 @@
+/* irontensor_b200 -- C ABI of the B200 (sm_100a) attention path for the IronTensor library.
+ *
+ * This is what a CUDA device behind IronTensor's op layer binds to.  Every entry point names the
+ * reference interface it stands in for (paths relative to the reference project's root).
+ * Conventions:
+ *   - plain C: opaque handles, raw pointers, sizes; no C++ or torch types.
+ *   - every call returns an it_status (0 = OK, negative = error); it_last_error() gives the text
+ *     of the calling thread's most recent failure.  Nothing throws, nothing aborts.
+ *   - tensor arguments are DEVICE pointers owned by the caller, contiguous row-major
+ *     [batch, heads, seq, head_dim] (the layout of src/ops/flash_attention.rs:65-70).
+ *   - compute calls only enqueue work on `stream` and return; results are valid after
+ *     it_stream_sync / it_event_wait, like work encoded into the reference's CommandBatch.
+ *   - compute calls allocate nothing: scratch comes from the caller's workspace.
+ *   - there is no CPU fallback: without a CUDA device it_ctx_create fails.
+ */
+#ifndef IRONTENSOR_B200_H
+#define IRONTENSOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct it_ctx it_ctx;       /* one per process and GPU; stands in for MetalContext (src/device.rs:10-37) */
+typedef struct it_stream it_stream; /* ordered work queue; stands in for a thread's CommandBatch (src/command_batch.rs:49-53) */
+typedef struct it_event it_event;   /* completion marker; stands in for the async command buffer handle (src/command_batch.rs:228-275) */
+
+typedef int32_t it_status;
+enum {
+  IT_OK = 0,
+  IT_ERR_INVALID_ARG = -1,       /* null pointer, negative size, undersized workspace */
+  IT_ERR_UNSUPPORTED_SHAPE = -2, /* head_dim outside 1..128 (assert at src/ops/flash_attention.rs:98) */
+  IT_ERR_PRECISION = -3,         /* dtype not handled (asserts at src/ops/flash_attention.rs:78-80) */
+  IT_ERR_ALIGNMENT = -4,         /* a tensor pointer is not 16-byte aligned */
+  IT_ERR_CUDA = -5,              /* a CUDA runtime or driver call failed */
+  IT_ERR_TIMEOUT = -6            /* a bounded wait inside a kernel ran out (see it_attention_status_poll) */
+};
+
+/* Storage precision of the tensors; arithmetic is fp32 either way (src/precision.rs:1-6;
+ * bf16 follows "read BF16, compute FP32, write BF16", src/shaders/bf16_ops.metal:8). */
+typedef enum { IT_F32 = 0, IT_BF16 = 1 } it_dtype;
+
+/* ---- context, streams, events ------------------------------------------------------------- */
+
+/* MetalContext::new / ::global (src/device.rs:17-29).  Fails with IT_ERR_CUDA when the device
+ * does not exist or is not an sm_100 part. */
+it_status it_ctx_create(int device, it_ctx** out);
+it_status it_ctx_destroy(it_ctx* ctx);
+/* Text of the calling thread's last error (never null). */
+const char* it_last_error(void);
+
+/* CommandBatch::begin (src/command_batch.rs:174-182): a new in-order queue. */
+it_status it_stream_create(it_ctx* ctx, it_stream** out);
+/* Adopts an existing cudaStream_t (0 = the legacy default stream) without owning it. */
+it_status it_stream_wrap(it_ctx* ctx, void* cuda_stream, it_stream** out);
+it_status it_stream_destroy(it_ctx* ctx, it_stream* stream);
+/* CommandBatch::sync / ::end (src/command_batch.rs:191-226): block until the queue drains. */
+it_status it_stream_sync(it_ctx* ctx, it_stream* stream);
+
+/* CommandBatch::commit_async / is_async_complete / wait_for_completion
+ * (src/command_batch.rs:228-275). */
+it_status it_event_create(it_ctx* ctx, it_event** out);
+it_status it_event_destroy(it_ctx* ctx, it_event* ev);
+it_status it_event_record(it_ctx* ctx, it_stream* stream, it_event* ev);
+it_status it_event_query(it_ctx* ctx, it_event* ev, int32_t* done);
+it_status it_event_wait(it_ctx* ctx, it_event* ev);
+/* Device time between two recorded, completed events (the profiler hook of
+ * src/profile/timer.rs:27-36, measured on the GPU instead of the host). */
+it_status it_event_elapsed_ms(it_ctx* ctx, it_event* start, it_event* stop, float* ms);
+
+/* ---- buffers ------------------------------------------------------------------------------ */
+
+/* Tensor::zeros' allocation (src/tensor.rs:63-84); zero bytes allocate one byte as there. */
+it_status it_buf_alloc(it_ctx* ctx, size_t bytes, void** out_dev);
+it_status it_buf_free(it_ctx* ctx, void* dev);
+/* Page-locked host memory for uploads/downloads that overlap with compute. */
+it_status it_host_alloc(it_ctx* ctx, size_t bytes, void** out_host);
+it_status it_host_free(it_ctx* ctx, void* host);
+/* Tensor::from_f32_slice (src/tensor.rs:90-118) and Tensor::as_f32_slice (src/tensor.rs:136-148):
+ * the reference's buffers are unified memory; here the copies are explicit and stream-ordered. */
+it_status it_buf_upload(it_ctx* ctx, it_stream* stream, void* dst_dev, const void* src_host, size_t bytes);
+it_status it_buf_download(it_ctx* ctx, it_stream* stream, void* dst_host, const void* src_dev, size_t bytes);
+it_status it_buf_memset_async(it_ctx* ctx, it_stream* stream, void* dev, int value, size_t bytes);
+
+/* ---- attention ---------------------------------------------------------------------------- */
+
+/* flash_attention(q, k, v, causal) (src/ops/flash_attention.rs:76-193; kernels
+ * src/shaders/flash_attention.metal:45-163 and :167-223).  O = softmax(mask(Q K^T / sqrt(D))) V.
+ * Adds what the reference lacks: bf16 tensors, and lse[B,H,S] (fp32, natural log of the row's sum
+ * of exp(scaled scores); may be null).  seq == 0 or batch*heads == 0 is a no-op returning IT_OK. */
+it_status it_flash_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t heads,
+                                 int32_t seq, int32_t head_dim, int32_t causal, const void* q, const void* k,
+                                 const void* v, void* o, float* lse);
+
+/* Scratch size for it_flash_attention_bwd with the same dtype and shape. */
+it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t batch, int32_t heads, int32_t seq,
+                                                 int32_t head_dim, size_t* out_bytes);
+
+/* attention_backward_recompute(grad_output, q, k, v) (src/train/helpers.rs:120-193).  The
+ * reference recomputes P from Q,K alone through eight S x S intermediates; this call recomputes
+ * it tile by tile from the forward's lse, so it also takes o and lse (what the training cache of
+ * src/train/cache.rs:10-15 gains).  The reference is always causal (helpers.rs:152); `causal`
+ * must match the forward that produced o and lse.  workspace: device memory of at least
+ * it_flash_attention_bwd_workspace_bytes, 256-byte aligned; its contents are overwritten. */
+it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t heads,
+                                 int32_t seq, int32_t head_dim, int32_t causal, const void* q, const void* k,
+                                 const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+                                 void* dk, void* dv, void* workspace, size_t workspace_bytes);
+
+/* Kernels never spin without bound: a wait that runs out (about one second) records a code in a
+ * device status word and the kernel winds down.  This call drains `stream`, returns the word in
+ * *device_status (0 = clean) and clears it.  Returns IT_ERR_TIMEOUT when the word was non-zero.
+ * (The reference never checks command-buffer errors; src/command_batch.rs:191-226.) */
+it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* device_status);
+
+/* How many kernels this library has launched on this context since it was created. */
+it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out);
+
+/* ---- self tests (no reference counterpart; they pin the hardware descriptors the kernels use) */
+
+/* One 128x128x128 bf16 MMA through the given operand path, result fp32 [128,128] row-major.
+ *   variant 0: A, B both K-major in shared memory (TMA)             a[128(M),128(K)], b[128(N),128(K)]
+ *   variant 1: A from tensor memory, B N-major in shared memory     a[M,K], b[128(K),128(N)]
+ *   variant 2: A K-major written by threads (swizzled), B N-major   a[M,K], b[K,N]
+ *   variant 3: A M-major written by threads (swizzled), B N-major   a[M,K], b[K,N]
+ * In every variant out = a * (b as K x N). */
+it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, const void* a_bf16,
+                           const void* b_bf16, float* out);
+/* Launches one CTA that waits `limit_ms` on a barrier nothing arrives on, so that the bounded-wait
+ * path can be checked: afterwards it_attention_status_poll reports a non-zero word. */
+it_status it_selftest_wait_timeout(it_ctx* ctx, it_stream* stream, int32_t limit_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IRONTENSOR_B200_H */

@@ -1,0 +1,341 @@
+// Causal / full scaled-dot-product attention forward for bf16 inputs on sm_100a.
+//
+// Replaces, for bf16 tensors with head_dim 64 or 128, the reference project's forward kernels
+// (src/shaders/flash_attention.metal:45-163 online softmax; :167-223 exact softmax) and adds the
+// per-row log-sum-exp output the fused backward needs.
+//
+// One CTA owns two consecutive 128-row query tiles of one (batch, head) slice and walks the key
+// tiles once, feeding both:
+//   warp 0      : TMA producer  - Q tiles once, then a ring of K and V tiles (128-byte swizzle)
+//   warp 1      : MMA issuer    - S_t = Q_t K^T and O_t += P_t V on tcgen05, accumulators in TMEM
+//   warp 2      : TMEM allocation / release
+//   warps 4-7   : softmax for query tile 0 (one thread per query row)
+//   warps 8-11  : softmax for query tile 1
+// While one softmax group works on its S tile the tensor core runs the other tile's MMAs.
+// Softmax runs in the exp2 domain with 1/sqrt(D)*log2(e) folded into one FMA; the running max is
+// only raised (and O rescaled in TMEM) when it would grow by more than 2^8, which keeps rescales
+// rare without loss of accuracy (fp32 accumulators hold the extra range).  P is written back over
+// S in TMEM as packed bf16 and consumed from there as the A operand of the P*V MMA.
+// Causal: key tiles above the diagonal are never loaded; only the diagonal tile is masked.
+// TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace it {
+
+template <int D>
+struct FwdTraits {
+  static constexpr int BM = 128;            // query rows per tile
+  static constexpr int BN = 128;            // keys per tile
+  static constexpr int STAGES = (D == 128) ? 2 : 4;
+  static constexpr int TILE_BYTES = BM * D * 2;          // one Q, K or V tile
+  static constexpr int BLOCK_BYTES = 128 * 128;          // one [128 x 64] bf16 swizzled block
+  static constexpr int NBLK = D / 64;                    // 64-column blocks per tile
+  static constexpr int SMEM_Q = 0;
+  static constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;
+  static constexpr int SMEM_V = SMEM_K + STAGES * TILE_BYTES;
+  static constexpr int SMEM_BAR = SMEM_V + STAGES * TILE_BYTES;
+  static constexpr int NUM_BARS = 2 + 4 * STAGES + 6;
+  static constexpr int SMEM_MISC = SMEM_BAR + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = SMEM_MISC + 16;
+  static constexpr int THREADS = 384;
+  static constexpr uint32_t TMEM_COLS = 512;
+};
+
+struct FwdParams {
+  __nv_bfloat16* o;     // [BH, S, D]
+  float* lse;           // [BH, S] or null
+  int* status;          // device status word
+  int S;
+  int BH;
+  int causal;
+  float scale_log2;     // 1/sqrt(D) * log2(e)
+};
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const FwdParams prm) {
+  using T = FwdTraits<D>;
+  using namespace ptx;
+  extern __shared__ __align__(1024) uint8_t smem[];
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::SMEM_BAR);
+  uint64_t* q_full = bars;                        // [2]
+  uint64_t* k_full = q_full + 2;                  // [STAGES]
+  uint64_t* k_empty = k_full + T::STAGES;
+  uint64_t* v_full = k_empty + T::STAGES;
+  uint64_t* v_empty = v_full + T::STAGES;
+  uint64_t* s_full = v_empty + T::STAGES;         // [2]
+  uint64_t* p_full = s_full + 2;                  // [2]
+  uint64_t* o_done = p_full + 2;                  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + T::SMEM_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::SMEM_MISC + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int S = prm.S;
+  const int n_kv_total = (S + T::BN - 1) / T::BN;
+  const int n_pairs = (S + 2 * T::BM - 1) / (2 * T::BM);
+  // Heaviest (last) query tiles of every head first.
+  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) / prm.BH;
+  const int bh = static_cast<int>(blockIdx.x) % prm.BH;
+  int n_kv[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt = 2 * pair + t;
+    n_kv[t] = (qt * T::BM < S) ? (prm.causal ? min(qt + 1, n_kv_total) : n_kv_total) : 0;
+  }
+  const int n_iter = max(n_kv[0], n_kv[1]);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if (smem_addr(smem) & 1023u) {
+      *abort_flag = 1;
+      atomicCAS(prm.status, 0, DEV_ERR_SMEM_ALIGN);
+    }
+    // An earlier CTA of this (or a previous) launch gave up on a wait: do not start, so that a
+    // launch that cannot make progress drains quickly instead of timing out CTA by CTA.
+    if (*reinterpret_cast<volatile int*>(prm.status) != 0) *abort_flag = 1;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_done[i], 1);
+    }
+    for (int i = 0; i < T::STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, T::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool bad_start = (*abort_flag != 0);
+
+  if (!bad_start) {
+    if (warp == 0) {
+      // ------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        for (int t = 0; t < 2; ++t) {
+          if (n_kv[t] == 0) continue;
+          mbar_arrive_expect_tx(&q_full[t], T::TILE_BYTES);
+          for (int b = 0; b < T::NBLK; ++b)
+            tma_load_3d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
+                        (2 * pair + t) * T::BM, bh);
+        }
+        for (int j = 0; j < n_iter; ++j) {
+          const int st = j % T::STAGES;
+          const uint32_t ph = (j / T::STAGES) & 1;
+          if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
+          mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
+          for (int b = 0; b < T::NBLK; ++b)
+            tma_load_3d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
+                        j * T::BN, bh);
+          if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
+          mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
+          for (int b = 0; b < T::NBLK; ++b)
+            tma_load_3d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
+                        j * T::BN, bh);
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------ MMA issuer (one thread)
+      if (lane == 0) {
+        constexpr uint32_t IDESC_S = make_idesc(128, 128, false, false);
+        constexpr uint32_t IDESC_PV = make_idesc(128, D, false, true);
+        const uint32_t q_addr = smem_addr(smem + T::SMEM_Q);
+        const uint32_t k_addr = smem_addr(smem + T::SMEM_K);
+        const uint32_t v_addr = smem_addr(smem + T::SMEM_V);
+        auto issue_s = [&](int t, int st) {   // S_t = Q_t * K_st^T, K-major operands
+          const uint64_t dq = make_sdesc(q_addr + t * T::TILE_BYTES, 16, 1024);
+          const uint64_t dk = make_sdesc(k_addr + st * T::TILE_BYTES, 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * T::BLOCK_BYTES + (kk & 3) * 32;
+            umma_ss(tmem_base + t * 128, sdesc_advance(dq, off), sdesc_advance(dk, off), IDESC_S, kk > 0);
+          }
+          umma_commit(&s_full[t]);
+        };
+        auto issue_pv = [&](int t, int st, bool first) {   // O_t += P_t * V_st, P from TMEM, V N-major
+          const uint64_t dv = make_sdesc(v_addr + st * T::TILE_BYTES, T::BLOCK_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < T::BN / 16; ++kk)
+            umma_ts(tmem_base + 256 + t * D, tmem_base + t * 128 + kk * 8, sdesc_advance(dv, kk * 2048), IDESC_PV,
+                    (!first || kk > 0) ? 1u : 0u);
+        };
+        bool ok = true;
+        // prologue: S_t(0)
+        ok = mbar_wait(&k_full[0], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (n_kv[t] == 0) continue;
+          ok = mbar_wait(&q_full[t], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(t, 0);
+        }
+        if (ok) umma_commit(&k_empty[0]);
+        for (int j = 0; j < n_iter && ok; ++j) {
+          const int st = j % T::STAGES;
+          const uint32_t ph = (j / T::STAGES) & 1;
+          const int st_n = (j + 1) % T::STAGES;
+          const uint32_t ph_n = ((j + 1) / T::STAGES) & 1;
+          const bool have_next = (j + 1 < n_iter);
+          if (have_next) ok = mbar_wait(&k_full[st_n], ph_n, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+          if (!ok) break;
+          ok = mbar_wait(&v_full[st], ph, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+          if (!ok) break;
+          for (int t = 0; t < 2; ++t) {
+            if (j >= n_kv[t]) continue;
+            ok = mbar_wait(&p_full[t], j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, st, j == 0);
+            if (j == n_kv[t] - 1) umma_commit(&o_done[t]);
+            if (j + 1 < n_kv[t]) issue_s(t, st_n);
+          }
+          if (!ok) break;
+          umma_commit(&v_empty[st]);
+          if (have_next) umma_commit(&k_empty[st_n]);
+        }
+      }
+    } else if (warp >= 4) {
+      // ------------------------------------------------------------ softmax + epilogue
+      const int t = (warp - 4) >> 2;
+      const int nkv = n_kv[t];
+      if (nkv > 0) {
+        const int qt = 2 * pair + t;
+        const int lane_base = (warp & 3) * 32;
+        const int q_row = qt * T::BM + lane_base + lane;
+        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + t * 128;
+        const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + 256 + t * D;
+        const float sl2 = prm.scale_log2;
+        float m_used = -INFINITY;
+        float l_sum = 0.f;
+        bool ok = true;
+        uint32_t r[32];
+        for (int j = 0; j < nkv; ++j) {
+          ok = mbar_wait(&s_full[t], j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const bool need_mask = (prm.causal && j == qt) || ((j + 1) * T::BN > S);
+          const int kbase = j * T::BN;
+          const int k_limit = prm.causal ? min(S - 1, q_row) : (S - 1);   // last visible key index
+          // pass 1: row maximum
+          float mx = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_x32(t_s + c * 32, r);
+            tmem_wait_ld();
+            if (need_mask) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (kbase + c * 32 + i <= k_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+            }
+          }
+          const float m_new = mx * sl2;
+          if (j == 0) {
+            m_used = m_new;
+          } else {
+            const bool grow = m_new > m_used + 8.0f;
+            if (__any_sync(0xffffffffu, grow)) {
+              const float m_next = fmaxf(m_used, m_new);
+              const float f = ex2(m_used - m_next);
+              l_sum *= f;
+              m_used = m_next;
+#pragma unroll 1
+              for (int c = 0; c < D / 32; ++c) {
+                tmem_ld_x32(t_o + c * 32, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+                tmem_st_x32(t_o + c * 32, r);
+              }
+              tmem_wait_st();
+            }
+          }
+          // pass 2: P = 2^(s*scale - m), packed bf16 written over S
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_x32(t_s + c * 32, r);
+            tmem_wait_ld();
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float p0 = ex2(fmaf(__uint_as_float(r[i]), sl2, -m_used));
+              float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sl2, -m_used));
+              if (need_mask) {
+                if (kbase + c * 32 + i > k_limit) p0 = 0.f;
+                if (kbase + c * 32 + i + 1 > k_limit) p1 = 0.f;
+              }
+              l_sum += p0 + p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+            tmem_st_x16(t_s + c * 16, pk);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&p_full[t]);
+        }
+        if (ok) {
+          ok = mbar_wait(&o_done[t], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+          tc_fence_after();
+          const float inv_l = 1.0f / l_sum;
+          __nv_bfloat16* orow = prm.o + (static_cast<size_t>(bh) * S + q_row) * D;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld_x32(t_o + c * 32, r);
+            tmem_wait_ld();
+            if (q_row < S) {
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                uint4 w;
+                w.x = pack_bf16(__uint_as_float(r[v4 * 8 + 0]) * inv_l, __uint_as_float(r[v4 * 8 + 1]) * inv_l);
+                w.y = pack_bf16(__uint_as_float(r[v4 * 8 + 2]) * inv_l, __uint_as_float(r[v4 * 8 + 3]) * inv_l);
+                w.z = pack_bf16(__uint_as_float(r[v4 * 8 + 4]) * inv_l, __uint_as_float(r[v4 * 8 + 5]) * inv_l);
+                w.w = pack_bf16(__uint_as_float(r[v4 * 8 + 6]) * inv_l, __uint_as_float(r[v4 * 8 + 7]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = w;
+              }
+            }
+          }
+          if (prm.lse != nullptr && q_row < S)
+            prm.lse[static_cast<size_t>(bh) * S + q_row] = (m_used + lg2(l_sum)) * 0.6931471805599453f;
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*abort_flag) {
+      // Let any TMA copy or MMA still in flight land before the CTA's memory goes away.
+      for (int i = 0; i < 50; ++i) __nanosleep(20000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+}  // namespace it

@@ -1,0 +1,547 @@
+// C ABI of the B200 attention path (declared in include/irontensor_b200.h): context, streams,
+// events, buffers, and the attention forward / backward dispatch onto the sm_100a kernels.
+// Host-side validation mirrors the reference's asserts (src/ops/flash_attention.rs:78-104) but
+// returns status codes instead of panicking.
+#include "../../include/irontensor_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <atomic>
+#include <cmath>
+#include <new>
+
+#include "fa_bwd_sm100.cuh"
+#include "fa_fwd_sm100.cuh"
+#include "fa_generic.cuh"
+#include "selftest_sm100.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+it_status fail(it_status code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define IT_CUDA(expr)                                                                              \
+  do {                                                                                             \
+    cudaError_t e_ = (expr);                                                                       \
+    if (e_ != cudaSuccess) return fail(IT_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_));      \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+struct it_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int* d_status = nullptr;      // device status word written by kernels whose waits run out
+  int* h_status = nullptr;      // pinned mirror
+  EncodeTiledFn encode = nullptr;
+  std::atomic<uint64_t> launches{0};
+};
+struct it_stream {
+  cudaStream_t s = nullptr;
+  bool owned = false;
+};
+struct it_event {
+  cudaEvent_t e = nullptr;
+};
+
+namespace {
+
+// [BH, S, D] bf16 row-major viewed as a 3-D tensor (d innermost); one box = 128 rows x 64 columns
+// of one head, written to shared memory with the 128-byte swizzle.  Rows past S read as zero.
+it_status make_tmap(it_ctx* ctx, CUtensorMap* map, const void* base, int64_t BH, int64_t S, int64_t D,
+                    int box_rows) {
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(BH)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(S) * D * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(IT_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+  return IT_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+it_status check_common(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S, int32_t D) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (dtype != IT_F32 && dtype != IT_BF16) return fail(IT_ERR_PRECISION, "dtype %d is not F32 or BF16", (int)dtype);
+  if (B < 0 || H < 0 || S < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  if (D < 1 || D > 128) return fail(IT_ERR_UNSUPPORTED_SHAPE, "head_dim must be in 1..128, got %d", D);
+  if (static_cast<int64_t>(B) * H > 65535)
+    return fail(IT_ERR_UNSUPPORTED_SHAPE, "batch*heads must be <= 65535, got %lld", (long long)B * H);
+  return IT_OK;
+}
+
+// The tensor-core kernels take bf16 tensors with head_dim 64 or 128 and at least one full tile.
+bool use_sm100_path(it_dtype dtype, int32_t S, int32_t D) {
+  return dtype == IT_BF16 && (D == 64 || D == 128) && S >= 128;
+}
+
+int round_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128; }
+
+template <typename ST>
+void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
+                        const void* v, void* o, float* lse) {
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  const dim3 grid((S + 63) / 64, BH);
+  const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
+  ST* oo = static_cast<ST*>(o);
+  switch (round_dp(D)) {
+    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
+    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
+    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
+    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
+  }
+  ctx->launches += 1;
+}
+
+template <typename ST>
+void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
+                        const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                        float* delta) {
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
+  const ST *oo = static_cast<const ST*>(o), *dd = static_cast<const ST*>(d_o);
+  const long long rows = static_cast<long long>(BH) * S;
+  it::fa_bwd_generic_delta_kernel<ST><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(oo, dd, delta, rows, D);
+  const dim3 grid((S + 3) / 4, BH);
+  it::fa_bwd_generic_kernel<ST, 0><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq),
+                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale);
+  it::fa_bwd_generic_kernel<ST, 1><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq),
+                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale);
+  ctx->launches += 3;
+}
+
+template <int D>
+it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causal, const void* q, const void* k,
+                           const void* v, void* o, float* lse) {
+  using T = it::FwdTraits<D>;
+  CUtensorMap mq, mk, mv;
+  it_status st;
+  if ((st = make_tmap(ctx, &mq, q, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, k, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, v, BH, S, D, 128)) != IT_OK) return st;
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    IT_CUDA(cudaFuncSetAttribute(it::fa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    attr_set[ctx->device & 15] = true;
+  }
+  it::FwdParams p;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.status = ctx->d_status;
+  p.S = S;
+  p.BH = BH;
+  p.causal = causal;
+  p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
+  const int n_pairs = (S + 255) / 256;
+  it::fa_fwd_sm100_kernel<D><<<static_cast<unsigned>(n_pairs) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+struct BwdWorkspace {
+  size_t dq_accum_off, lse2_off, delta_off, total;
+  int S_pad;
+};
+BwdWorkspace bwd_workspace_layout(it_dtype dtype, int64_t BH, int64_t S, int64_t D) {
+  BwdWorkspace w{};
+  auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+  if (use_sm100_path(dtype, static_cast<int32_t>(S), static_cast<int32_t>(D))) {
+    w.S_pad = static_cast<int>((S + 127) / 128 * 128);
+    w.dq_accum_off = 0;
+    w.lse2_off = up(static_cast<size_t>(BH) * S * D * 4);
+    w.delta_off = w.lse2_off + up(static_cast<size_t>(BH) * w.S_pad * 4);
+    w.total = w.delta_off + up(static_cast<size_t>(BH) * w.S_pad * 4);
+  } else {
+    w.S_pad = static_cast<int>(S);
+    w.delta_off = 0;
+    w.total = up(static_cast<size_t>(BH) * S * 4);
+  }
+  if (w.total == 0) w.total = 256;
+  return w;
+}
+
+template <int D>
+it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causal, const void* q, const void* k,
+                           const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk,
+                           void* dv, uint8_t* ws, const BwdWorkspace& w) {
+  using T = it::BwdTraits<D>;
+  CUtensorMap mq, mk, mv, mdo;
+  it_status st;
+  if ((st = make_tmap(ctx, &mq, q, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, k, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, v, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mdo, d_o, BH, S, D, 128)) != IT_OK) return st;
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    IT_CUDA(cudaFuncSetAttribute(it::fa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    attr_set[ctx->device & 15] = true;
+  }
+  float* dq_accum = reinterpret_cast<float*>(ws + w.dq_accum_off);
+  float* lse2 = reinterpret_cast<float*>(ws + w.lse2_off);
+  float* delta = reinterpret_cast<float*>(ws + w.delta_off);
+  const size_t n_dq = static_cast<size_t>(BH) * S * D;
+  IT_CUDA(cudaMemsetAsync(dq_accum, 0, n_dq * 4, s));
+  const long long rows_pad = static_cast<long long>(BH) * w.S_pad;
+  it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad + 7) / 8), 256, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, S, w.S_pad, BH);
+  it::BwdParams p;
+  p.lse2_pad = lse2;
+  p.delta_pad = delta;
+  p.dq_accum = dq_accum;
+  p.dk = static_cast<__nv_bfloat16*>(dk);
+  p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.status = ctx->d_status;
+  p.S = S;
+  p.S_pad = w.S_pad;
+  p.BH = BH;
+  p.causal = causal;
+  p.scale = 1.0f / sqrtf(static_cast<float>(D));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  const int n_kt = (S + 127) / 128;
+  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  const size_t n4 = n_dq / 4;
+  it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
+      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale);
+  ctx->launches += 3;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* it_last_error(void) { return g_err; }
+
+it_status it_ctx_create(int device, it_ctx** out) {
+  if (out == nullptr) return fail(IT_ERR_INVALID_ARG, "out is null");
+  *out = nullptr;
+  int count = 0;
+  IT_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) return fail(IT_ERR_CUDA, "CUDA device %d not present (%d visible)", device, count);
+  IT_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  IT_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(IT_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                prop.minor);
+  it_ctx* c = new (std::nothrow) it_ctx;
+  if (c == nullptr) return fail(IT_ERR_CUDA, "out of host memory");
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+    delete c;
+    return fail(IT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  c->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess || cudaMemset(c->d_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess) {
+    delete c;
+    return fail(IT_ERR_CUDA, "could not allocate the status word");
+  }
+  *out = c;
+  return IT_OK;
+}
+
+it_status it_ctx_destroy(it_ctx* ctx) {
+  if (ctx == nullptr) return IT_OK;
+  cudaSetDevice(ctx->device);
+  cudaFree(ctx->d_status);
+  cudaFreeHost(ctx->h_status);
+  delete ctx;
+  return IT_OK;
+}
+
+it_status it_stream_create(it_ctx* ctx, it_stream** out) {
+  if (ctx == nullptr || out == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  it_stream* s = new (std::nothrow) it_stream;
+  if (s == nullptr) return fail(IT_ERR_CUDA, "out of host memory");
+  cudaError_t e = cudaStreamCreateWithFlags(&s->s, cudaStreamNonBlocking);
+  if (e != cudaSuccess) {
+    delete s;
+    return fail(IT_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+  }
+  s->owned = true;
+  *out = s;
+  return IT_OK;
+}
+
+it_status it_stream_wrap(it_ctx* ctx, void* cuda_stream, it_stream** out) {
+  if (ctx == nullptr || out == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  it_stream* s = new (std::nothrow) it_stream;
+  if (s == nullptr) return fail(IT_ERR_CUDA, "out of host memory");
+  s->s = static_cast<cudaStream_t>(cuda_stream);
+  s->owned = false;
+  *out = s;
+  return IT_OK;
+}
+
+it_status it_stream_destroy(it_ctx* ctx, it_stream* stream) {
+  if (stream == nullptr) return IT_OK;
+  if (ctx != nullptr) cudaSetDevice(ctx->device);
+  if (stream->owned) cudaStreamDestroy(stream->s);
+  delete stream;
+  return IT_OK;
+}
+
+it_status it_stream_sync(it_ctx* ctx, it_stream* stream) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaStreamSynchronize(stream->s));
+  return IT_OK;
+}
+
+it_status it_event_create(it_ctx* ctx, it_event** out) {
+  if (ctx == nullptr || out == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  it_event* ev = new (std::nothrow) it_event;
+  if (ev == nullptr) return fail(IT_ERR_CUDA, "out of host memory");
+  cudaError_t e = cudaEventCreate(&ev->e);
+  if (e != cudaSuccess) {
+    delete ev;
+    return fail(IT_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
+  }
+  *out = ev;
+  return IT_OK;
+}
+
+it_status it_event_destroy(it_ctx* ctx, it_event* ev) {
+  (void)ctx;
+  if (ev == nullptr) return IT_OK;
+  cudaEventDestroy(ev->e);
+  delete ev;
+  return IT_OK;
+}
+
+it_status it_event_record(it_ctx* ctx, it_stream* stream, it_event* ev) {
+  if (ctx == nullptr || stream == nullptr || ev == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaEventRecord(ev->e, stream->s));
+  return IT_OK;
+}
+
+it_status it_event_query(it_ctx* ctx, it_event* ev, int32_t* done) {
+  if (ctx == nullptr || ev == nullptr || done == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  cudaError_t e = cudaEventQuery(ev->e);
+  if (e == cudaSuccess) {
+    *done = 1;
+  } else if (e == cudaErrorNotReady) {
+    *done = 0;
+  } else {
+    return fail(IT_ERR_CUDA, "cudaEventQuery: %s", cudaGetErrorString(e));
+  }
+  return IT_OK;
+}
+
+it_status it_event_wait(it_ctx* ctx, it_event* ev) {
+  if (ctx == nullptr || ev == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaEventSynchronize(ev->e));
+  return IT_OK;
+}
+
+it_status it_event_elapsed_ms(it_ctx* ctx, it_event* start, it_event* stop, float* ms) {
+  if (ctx == nullptr || start == nullptr || stop == nullptr || ms == nullptr)
+    return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaEventElapsedTime(ms, start->e, stop->e));
+  return IT_OK;
+}
+
+it_status it_buf_alloc(it_ctx* ctx, size_t bytes, void** out_dev) {
+  if (ctx == nullptr || out_dev == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  IT_CUDA(cudaMalloc(out_dev, bytes == 0 ? 1 : bytes));
+  return IT_OK;
+}
+
+it_status it_buf_free(it_ctx* ctx, void* dev) {
+  if (ctx == nullptr) return fail(IT_ERR_INVALID_ARG, "null context");
+  if (dev != nullptr) IT_CUDA(cudaFree(dev));
+  return IT_OK;
+}
+
+it_status it_host_alloc(it_ctx* ctx, size_t bytes, void** out_host) {
+  if (ctx == nullptr || out_host == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  IT_CUDA(cudaMallocHost(out_host, bytes == 0 ? 1 : bytes));
+  return IT_OK;
+}
+
+it_status it_host_free(it_ctx* ctx, void* host) {
+  if (ctx == nullptr) return fail(IT_ERR_INVALID_ARG, "null context");
+  if (host != nullptr) IT_CUDA(cudaFreeHost(host));
+  return IT_OK;
+}
+
+it_status it_buf_upload(it_ctx* ctx, it_stream* stream, void* dst_dev, const void* src_host, size_t bytes) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (bytes == 0) return IT_OK;
+  if (dst_dev == nullptr || src_host == nullptr) return fail(IT_ERR_INVALID_ARG, "null buffer");
+  IT_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, stream->s));
+  return IT_OK;
+}
+
+it_status it_buf_download(it_ctx* ctx, it_stream* stream, void* dst_host, const void* src_dev, size_t bytes) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (bytes == 0) return IT_OK;
+  if (dst_host == nullptr || src_dev == nullptr) return fail(IT_ERR_INVALID_ARG, "null buffer");
+  IT_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, stream->s));
+  return IT_OK;
+}
+
+it_status it_buf_memset_async(it_ctx* ctx, it_stream* stream, void* dev, int value, size_t bytes) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (bytes == 0) return IT_OK;
+  if (dev == nullptr) return fail(IT_ERR_INVALID_ARG, "null buffer");
+  IT_CUDA(cudaMemsetAsync(dev, value, bytes, stream->s));
+  return IT_OK;
+}
+
+it_status it_flash_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
+                                 int32_t D, int32_t causal, const void* q, const void* k, const void* v, void* o,
+                                 float* lse) {
+  it_status st = check_common(ctx, stream, dtype, B, H, S, D);
+  if (st != IT_OK) return st;
+  const int BH = B * H;
+  if (S == 0 || BH == 0) return IT_OK;   // src/ops/flash_attention.rs:102-104
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(IT_ERR_ALIGNMENT, "q, k, v and o must be 16-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  if (use_sm100_path(dtype, S, D)) {
+    return D == 128 ? launch_fwd_sm100<128>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, lse)
+                    : launch_fwd_sm100<64>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, lse);
+  }
+  if (dtype == IT_F32)
+    launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse);
+  else
+    launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse);
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int32_t H, int32_t S, int32_t D,
+                                                 size_t* out_bytes) {
+  if (out_bytes == nullptr) return fail(IT_ERR_INVALID_ARG, "out_bytes is null");
+  if (dtype != IT_F32 && dtype != IT_BF16) return fail(IT_ERR_PRECISION, "dtype %d is not F32 or BF16", (int)dtype);
+  if (B < 0 || H < 0 || S < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  if (D < 1 || D > 128) return fail(IT_ERR_UNSUPPORTED_SHAPE, "head_dim must be in 1..128, got %d", D);
+  *out_bytes = bwd_workspace_layout(dtype, static_cast<int64_t>(B) * H, S, D).total;
+  return IT_OK;
+}
+
+it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
+                                 int32_t D, int32_t causal, const void* q, const void* k, const void* v, const void* o,
+                                 const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
+                                 size_t workspace_bytes) {
+  it_status st = check_common(ctx, stream, dtype, B, H, S, D);
+  if (st != IT_OK) return st;
+  const int BH = B * H;
+  if (S == 0 || BH == 0) return IT_OK;
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || d_o == nullptr || lse == nullptr ||
+      dq == nullptr || dk == nullptr || dv == nullptr)
+    return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
+  const BwdWorkspace w = bwd_workspace_layout(dtype, BH, S, D);
+  if (workspace == nullptr || workspace_bytes < w.total)
+    return fail(IT_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return fail(IT_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (use_sm100_path(dtype, S, D)) {
+    return D == 128 ? launch_bwd_sm100<128>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w)
+                    : launch_bwd_sm100<64>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w);
+  }
+  float* delta = reinterpret_cast<float*>(ws + w.delta_off);
+  if (dtype == IT_F32)
+    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta);
+  else
+    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta);
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* device_status) {
+  if (ctx == nullptr || stream == nullptr || device_status == nullptr)
+    return fail(IT_ERR_INVALID_ARG, "null argument");
+  IT_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream->s));
+  IT_CUDA(cudaStreamSynchronize(stream->s));
+  *device_status = *ctx->h_status;
+  if (*device_status != 0) {
+    IT_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), stream->s));
+    IT_CUDA(cudaStreamSynchronize(stream->s));
+    return fail(IT_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (device status %d)", *device_status);
+  }
+  return IT_OK;
+}
+
+it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out) {
+  if (ctx == nullptr || out == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  *out = ctx->launches.load();
+  return IT_OK;
+}
+
+it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, const void* a_bf16, const void* b_bf16,
+                           float* out) {
+  if (ctx == nullptr || stream == nullptr || a_bf16 == nullptr || b_bf16 == nullptr || out == nullptr)
+    return fail(IT_ERR_INVALID_ARG, "null argument");
+  if (variant < 0 || variant > 3) return fail(IT_ERR_INVALID_ARG, "variant must be 0..3");
+  if (!aligned16(a_bf16) || !aligned16(b_bf16)) return fail(IT_ERR_ALIGNMENT, "operands must be 16-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  CUtensorMap ma, mb;
+  it_status st;
+  if ((st = make_tmap(ctx, &ma, a_bf16, 1, 128, 128, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mb, b_bf16, 1, 128, 128, 128)) != IT_OK) return st;
+  const int smem = 4 * 128 * 128 + 64;
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(a_bf16);
+#define IT_SELFTEST_CASE(V)                                                                                     \
+  case V:                                                                                                       \
+    IT_CUDA(cudaFuncSetAttribute(it::umma_selftest_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    it::umma_selftest_kernel<V><<<1, 128, smem, stream->s>>>(ma, mb, a, out, ctx->d_status);                    \
+    break;
+  switch (variant) {
+    IT_SELFTEST_CASE(0)
+    IT_SELFTEST_CASE(1)
+    IT_SELFTEST_CASE(2)
+    IT_SELFTEST_CASE(3)
+  }
+#undef IT_SELFTEST_CASE
+  ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+it_status it_selftest_wait_timeout(it_ctx* ctx, it_stream* stream, int32_t limit_ms) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  if (limit_ms < 1 || limit_ms > 1000) return fail(IT_ERR_INVALID_ARG, "limit_ms must be in 1..1000");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  it::wait_timeout_selftest_kernel<<<1, 32, 0, stream->s>>>(ctx->d_status,
+                                                           static_cast<unsigned long long>(limit_ms) * 1000000ull);
+  ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,360 @@
+"""Host-side mirror of the reference's attention interface, on top of the C ABI.
+
+Same names, argument meaning and error behaviour as the reference (paths relative to its root):
+  Precision, Tensor            src/precision.rs:1-29, src/tensor.rs:11-300
+  CommandBatch                 src/command_batch.rs:167-391
+  flash_attention              src/ops/flash_attention.rs:76-193     [B,H,S,D]
+  attention                    src/ops/attention.rs:286-377          [B,S,H,D]
+  attention_backward_recompute src/train/helpers.rs:120-193          [B,H,S,D]
+Where the reference asserts (panics), these raise AssertionError with the same message.
+
+torch is used for plumbing only: device memory, the current CUDA stream and pinned host buffers.
+All arithmetic runs in libirontensor_b200.so; if that library cannot be loaded, or no CUDA device
+is present, every op raises -- there is no fallback.
+"""
+import ctypes
+import enum
+import threading
+
+import numpy as np
+
+from . import _lib, synth
+
+
+class Precision(enum.Enum):
+    FP32 = 0
+    BF16 = 1
+
+    def byte_size(self):
+        return 4 if self is Precision.FP32 else 2
+
+
+_state = threading.local()
+_ctx_lock = threading.Lock()
+_ctxs = {}
+
+
+def _torch():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("irontensor_b200 needs a CUDA device (sm_100a); none is visible and there is no fallback")
+    return torch
+
+
+class _Context:
+    """Per-device library context (the reference's MetalContext::global, src/device.rs:15-29)."""
+
+    def __init__(self, device):
+        self.lib = _lib.load()
+        self.device = device
+        h = ctypes.c_void_p()
+        _lib.check(self.lib.it_ctx_create(device, ctypes.byref(h)))
+        self.handle = h
+        self._streams = {}
+
+    def stream(self):
+        """it_stream wrapping torch's current stream on this device."""
+        torch = _torch()
+        raw_stream = torch.cuda.current_stream(self.device).cuda_stream
+        s = self._streams.get(raw_stream)
+        if s is None:
+            s = ctypes.c_void_p()
+            _lib.check(self.lib.it_stream_wrap(self.handle, ctypes.c_void_p(raw_stream), ctypes.byref(s)))
+            self._streams[raw_stream] = s
+        return s
+
+    def launch_count(self):
+        n = ctypes.c_uint64()
+        _lib.check(self.lib.it_ctx_launch_count(self.handle, ctypes.byref(n)))
+        return n.value
+
+    def poll_status(self):
+        """Drains the current stream; raises ITError(IT_ERR_TIMEOUT) if a kernel's wait ran out."""
+        st = ctypes.c_int32()
+        rc = self.lib.it_attention_status_poll(self.handle, self.stream(), ctypes.byref(st))
+        _lib.check(rc)
+        return st.value
+
+
+def context(device=None):
+    torch = _torch()
+    if device is None:
+        device = torch.cuda.current_device()
+    with _ctx_lock:
+        c = _ctxs.get(device)
+        if c is None:
+            c = _Context(device)
+            _ctxs[device] = c
+        return c
+
+
+class CommandBatch:
+    """The reference batches encoded work per thread and flushes on sync (src/command_batch.rs:167-391).
+    Here work is enqueued on the thread's current CUDA stream as soon as an op is called; these
+    functions keep the same call sites meaningful."""
+
+    @staticmethod
+    def begin():
+        _state.active = True
+
+    @staticmethod
+    def is_active():
+        return getattr(_state, "active", False)
+
+    @staticmethod
+    def sync():
+        c = context()
+        _lib.check(c.lib.it_stream_sync(c.handle, c.stream()))
+
+    @staticmethod
+    def end():
+        CommandBatch.sync()
+        _state.active = False
+
+    @staticmethod
+    def commit_async():
+        c = context()
+        ev = ctypes.c_void_p()
+        _lib.check(c.lib.it_event_create(c.handle, ctypes.byref(ev)))
+        _lib.check(c.lib.it_event_record(c.handle, c.stream(), ev))
+        old = getattr(_state, "pending", None)
+        if old is not None:
+            c.lib.it_event_destroy(c.handle, old)
+        _state.pending = ev
+        _state.active = False
+
+    @staticmethod
+    def is_async_complete():
+        ev = getattr(_state, "pending", None)
+        if ev is None:
+            return True
+        c = context()
+        done = ctypes.c_int32()
+        _lib.check(c.lib.it_event_query(c.handle, ev, ctypes.byref(done)))
+        return bool(done.value)
+
+    @staticmethod
+    def wait_for_completion():
+        ev = getattr(_state, "pending", None)
+        if ev is None:
+            return
+        c = context()
+        _lib.check(c.lib.it_event_wait(c.handle, ev))
+        c.lib.it_event_destroy(c.handle, ev)
+        _state.pending = None
+
+
+class Tensor:
+    """Device-resident tensor: buffer + shape + precision (src/tensor.rs:11-15).
+
+    The reference's buffers are unified memory, so `as_f32_slice` aliases GPU memory
+    (src/tensor.rs:136-148); here it synchronises the stream and copies device -> host."""
+
+    def __init__(self, data, shape, precision):
+        self._data = data            # flat torch CUDA tensor (float32 or bfloat16)
+        self._shape = list(shape)
+        self._precision = precision
+        self.lse = None              # side output of flash_attention: Tensor [B,H,S] fp32
+
+    # -- constructors (src/tensor.rs:63-118, 205-240)
+    @staticmethod
+    def zeros(shape, precision=Precision.FP32):
+        torch = _torch()
+        dt = torch.float32 if precision is Precision.FP32 else torch.bfloat16
+        n = int(np.prod(shape)) if len(shape) else 1
+        return Tensor(torch.zeros(max(n, 1), dtype=dt, device="cuda")[:n], shape, precision)
+
+    @staticmethod
+    def from_f32_slice(data, shape):
+        torch = _torch()
+        a = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        n = int(np.prod(shape))
+        assert a.size == n, f"Data length {a.size} does not match shape {list(shape)} (numel={n})"
+        return Tensor(torch.from_numpy(a).to("cuda", non_blocking=False), shape, Precision.FP32)
+
+    @staticmethod
+    def from_bf16_slice(bits, shape):
+        torch = _torch()
+        a = np.ascontiguousarray(bits, dtype=np.uint16).reshape(-1)
+        n = int(np.prod(shape))
+        assert a.size == n, f"Data length {a.size} does not match shape {list(shape)} (numel={n})"
+        t = torch.from_numpy(a.view(np.int16)).to("cuda").view(torch.bfloat16)
+        return Tensor(t, shape, Precision.BF16)
+
+    @staticmethod
+    def from_f32_as_bf16(data, shape):
+        return Tensor.from_bf16_slice(synth.f32_to_bf16_bits(np.asarray(data, dtype=np.float32).reshape(-1)), shape)
+
+    # -- accessors
+    def shape(self):
+        return list(self._shape)
+
+    def precision(self):
+        return self._precision
+
+    def numel(self):
+        return int(np.prod(self._shape)) if self._shape else 1
+
+    def byte_size(self):
+        return self.numel() * self._precision.byte_size()
+
+    def is_bf16(self):
+        return self._precision is Precision.BF16
+
+    def is_f32(self):
+        return self._precision is Precision.FP32
+
+    def data_ptr(self):
+        return self._data.data_ptr()
+
+    def torch(self):
+        return self._data.view(self._shape)
+
+    def as_f32_slice(self):
+        assert self._precision is Precision.FP32, "Tensor is not FP32"
+        return self._data.cpu().numpy()
+
+    def as_bf16_slice(self):
+        assert self._precision is Precision.BF16, "Tensor is not BF16"
+        torch = _torch()
+        return self._data.view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def to_f32_host(self):
+        """Values as fp32 on the host, whatever the storage precision."""
+        if self._precision is Precision.FP32:
+            return self.as_f32_slice().reshape(self._shape)
+        return synth.bf16_bits_to_f32(self.as_bf16_slice()).reshape(self._shape)
+
+    def view(self, new_shape):
+        n = int(np.prod(new_shape))
+        assert n == self.numel(), f"Cannot view tensor with {self.numel()} elements as shape {list(new_shape)}"
+        t = Tensor(self._data, new_shape, self._precision)
+        return t
+
+    def to_bf16(self):
+        if self._precision is Precision.BF16:
+            return Tensor(self._data.clone(), self._shape, Precision.BF16)
+        return Tensor.from_f32_as_bf16(self.as_f32_slice(), self._shape)
+
+    def to_f32(self):
+        torch = _torch()
+        return Tensor(self._data.to(torch.float32), self._shape, Precision.FP32)
+
+
+def _dtype_code(p):
+    return _lib.IT_F32 if p is Precision.FP32 else _lib.IT_BF16
+
+
+class raw:
+    """Thin typed wrappers over the two compute entry points, taking raw device pointers."""
+
+    @staticmethod
+    def fwd(dtype, B, H, S, D, causal, q, k, v, o, lse, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_flash_attention_fwd(c.handle, c.stream(), dtype, B, H, S, D, int(causal), q, k, v, o, lse))
+
+    @staticmethod
+    def bwd_workspace_bytes(dtype, B, H, S, D):
+        n = ctypes.c_size_t()
+        _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))
+        return n.value
+
+    @staticmethod
+    def bwd(dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, ws, ws_bytes, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_flash_attention_bwd(c.handle, c.stream(), dtype, B, H, S, D, int(causal), q, k, v, o, d_o,
+                                                lse, dq, dk, dv, ws, ws_bytes))
+
+
+_workspaces = {}
+
+
+def _workspace(nbytes):
+    """Grow-only scratch buffer per device (the ops allocate outputs like the reference does; the
+    C ABI itself never allocates)."""
+    torch = _torch()
+    dev = torch.cuda.current_device()
+    w = _workspaces.get(dev)
+    if w is None or w.numel() < nbytes:
+        w = torch.empty(max(nbytes, 256), dtype=torch.uint8, device="cuda")
+        _workspaces[dev] = w
+    return w
+
+
+def flash_attention(q, k, v, causal):
+    """FlashAttention forward on [batch, heads, seq, head_dim] (src/ops/flash_attention.rs:76-193).
+
+    Accepts FP32 tensors like the reference and additionally BF16 (all three alike).  The per-row
+    log-sum-exp the fused backward needs is attached to the result as `.lse`."""
+    p = q.precision()
+    assert p in (Precision.FP32, Precision.BF16)
+    assert k.precision() is p and v.precision() is p, "Q, K and V must have the same precision"
+    qs, ks, vs = q.shape(), k.shape(), v.shape()
+    assert len(qs) == 4, "Q must be 4D [batch, heads, seq, head_dim]"
+    assert len(ks) == 4, "K must be 4D [batch, heads, seq, head_dim]"
+    assert len(vs) == 4, "V must be 4D [batch, heads, seq, head_dim]"
+    assert qs == ks, "Q and K must have same shape"
+    assert qs == vs, "Q and V must have same shape"
+    B, H, S, D = qs
+    assert D <= 128, "head_dim must be <= 128"
+    out = Tensor.zeros([B, H, S, D], p)
+    out.lse = Tensor.zeros([B, H, S], Precision.FP32)
+    if S == 0 or B * H == 0:
+        return out
+    raw.fwd(_dtype_code(p), B, H, S, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+            out.lse.data_ptr())
+    return out
+
+
+def attention(q, k, v, causal):
+    """Scaled dot-product attention on [batch, seq, heads, head_dim] (src/ops/attention.rs:286-377).
+
+    Same math as flash_attention; the layout change is done around the fused kernel.  The
+    reference lets K/V have another sequence length when not causal; that case is not taken here."""
+    p = q.precision()
+    assert k.precision() is p and v.precision() is p
+    qs, ks, vs = q.shape(), k.shape(), v.shape()
+    assert len(qs) == 4, "Q must be 4D [batch, seq, heads, dim]"
+    assert len(ks) == 4, "K must be 4D [batch, seq, heads, dim]"
+    assert len(vs) == 4, "V must be 4D [batch, seq, heads, dim]"
+    B, Sq, H, D = qs
+    assert ks[0] == B and vs[0] == B, "Batch size mismatch"
+    assert ks[2] == H and vs[2] == H, "Num heads mismatch"
+    assert ks[3] == D and vs[3] == D, "Head dim mismatch"
+    assert vs[1] == ks[1], "K and V seq_len must match"
+    if B == 0 or Sq == 0 or ks[1] == 0:
+        return Tensor.zeros([B, Sq, H, D], p)
+    if ks[1] != Sq:
+        raise NotImplementedError("attention(): K/V sequence length differs from Q's; only self-attention is fused")
+
+    def to_bhsd(t):
+        return Tensor(t.torch().permute(0, 2, 1, 3).contiguous().view(-1), [B, H, Sq, D], p)
+
+    o = flash_attention(to_bhsd(q), to_bhsd(k), to_bhsd(v), causal)
+    return Tensor(o.torch().permute(0, 2, 1, 3).contiguous().view(-1), [B, Sq, H, D], p)
+
+
+def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=True):
+    """(dQ, dK, dV) on [batch, heads, seq, head_dim] (src/train/helpers.rs:120-193).
+
+    The reference takes (grad_output, q, k, v) and is always causal.  Pass the forward's `o` and
+    `lse` (flash_attention's result and its `.lse`) to skip the recomputation; without them the
+    forward is run again here, which is what "recompute" means for the fused path."""
+    p = q.precision()
+    for t in (grad_output, k, v):
+        assert t.precision() is p, "all tensors must have the same precision"
+    B, H, S, D = q.shape()
+    for t in (grad_output, k, v):
+        assert t.shape() == [B, H, S, D], "shape mismatch"
+    dq, dk, dv = Tensor.zeros([B, H, S, D], p), Tensor.zeros([B, H, S, D], p), Tensor.zeros([B, H, S, D], p)
+    if S == 0 or B * H == 0:
+        return dq, dk, dv
+    if o is None or lse is None:
+        o = flash_attention(q, k, v, causal)
+        lse = o.lse
+    code = _dtype_code(p)
+    nbytes = raw.bwd_workspace_bytes(code, B, H, S, D)
+    ws = _workspace(nbytes)
+    raw.bwd(code, B, H, S, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(),
+            lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
+    return dq, dk, dv

@@ -1,0 +1,191 @@
+"""CPU tests of the oracle itself: against the golden vectors produced by the reference's own
+shader sources, against those sources directly where oracle/_ref was built, against an independent
+fp64 formulation and finite differences, and of the bf16 rounding rule."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from irontensor_b200 import synth
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def gold(name):
+    return np.load(os.path.join(GOLD, name + ".npz"))
+
+
+def seeded(seed, B, H, S, D, with_do=True):
+    return [t.reshape(B, H, S, D) for t in synth.attention_inputs(seed, B, H, S, D, with_do=with_do)]
+
+
+# ---------------------------------------------------------------- golden vectors (bit-exact)
+def test_golden_flash_kat1():
+    g = gold("flash_kat1")
+    assert np.array_equal(ol.fwd(g["q"], g["k"], g["v"], True)[0], g["o_causal"])
+    assert np.array_equal(ol.fwd(g["q"], g["k"], g["v"], False)[0], g["o_full"])
+
+
+def test_golden_flash_kat2():
+    g = gold("flash_kat2")
+    assert np.array_equal(ol.fwd(g["q"], g["k"], g["v"], True)[0], g["o_causal"])
+
+
+def test_golden_backward_kat():
+    g = gold("bwd_kat")
+    dq, dk, dv = ol.bwd(g["q"], g["k"], g["v"], g["d_o"])
+    assert np.array_equal(dq, g["dq"]) and np.array_equal(dk, g["dk"]) and np.array_equal(dv, g["dv"])
+    assert np.array_equal(ol.fwd(g["q"], g["k"], g["v"], True)[0], g["o_causal"])
+
+
+def test_golden_tiled_kernel_seeded():
+    g = gold("tiled_seeded")
+    q, k, v = seeded(int(g["seed"]), 1, 2, 300, 64, with_do=False)
+    assert np.array_equal(ol.fwd(q, k, v, True)[0], g["o_causal"])
+    assert np.array_equal(ol.fwd(q, k, v, False)[0], g["o_full"])
+
+
+def test_golden_decode_prefix_seeded():
+    g = gold("decode_seeded")
+    q, k, v = seeded(int(g["seed"]), 1, 4, 119, 64, with_do=False)
+    assert np.array_equal(ol.fwd(q, k, v, True)[0], g["o_causal"])
+
+
+def test_golden_backward_seeded():
+    g = gold("bwd_seeded")
+    q, k, v, d_o = seeded(int(g["seed"]), 1, 2, 40, 16)
+    for got, name in zip(ol.bwd(q, k, v, d_o), ("dq", "dk", "dv")):
+        assert np.array_equal(got, g[name]), name
+
+
+# ---------------------------------------------------------------- the reference's sources, live
+needs_ref = pytest.mark.skipif(ol.reference() is None, reason="oracle/_ref not built (no reference tree)")
+
+
+@needs_ref
+@pytest.mark.parametrize("shape,kernel", [((2, 4, 32, 16), 0), ((1, 2, 40, 16), 2), ((1, 2, 257, 64), 0),
+                                          ((2, 2, 33, 128), 1), ((1, 4, 20, 64), 0), ((1, 1, 256, 64), 0)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_forward_equals_reference_sources(shape, kernel, causal):
+    q, k, v = seeded(21, *shape, with_do=False)
+    assert np.array_equal(ol.fwd(q, k, v, causal, kernel)[0], ol.ref_fwd(q, k, v, causal, kernel))
+
+
+@needs_ref
+@pytest.mark.parametrize("shape", [(2, 4, 16, 8), (1, 2, 40, 16), (1, 1, 130, 32)])
+def test_backward_equals_reference_sources(shape):
+    q, k, v, d_o = seeded(22, *shape)
+    for a, b in zip(ol.bwd(q, k, v, d_o), ol.ref_bwd(q, k, v, d_o)):
+        assert np.array_equal(a, b)
+
+
+@needs_ref
+def test_backward_equals_reference_sources_threadgroup_softmax():
+    # S >= 256 makes the reference pick its 256-lane softmax kernels (src/ops/softmax.rs:196).
+    q, k, v, d_o = seeded(23, 1, 1, 256, 16)
+    for a, b in zip(ol.bwd(q, k, v, d_o), ol.ref_bwd(q, k, v, d_o)):
+        assert np.array_equal(a, b)
+
+
+# ---------------------------------------------------------------- independent math
+def sdpa_f64(q, k, v, d_o, causal):
+    q, k, v, d_o = (x.astype(np.float64) for x in (q, k, v, d_o))
+    S, D = q.shape[-2:]
+    s = q @ np.swapaxes(k, -1, -2) / np.sqrt(D)
+    if causal:
+        s = np.where(np.tril(np.ones((S, S), bool)), s, -np.inf)
+    m = s.max(-1, keepdims=True)
+    e = np.exp(s - m)
+    l = e.sum(-1, keepdims=True)
+    p = e / l
+    o = p @ v
+    lse = (m + np.log(l))[..., 0]
+    dv = np.swapaxes(p, -1, -2) @ d_o
+    dp = d_o @ np.swapaxes(v, -1, -2)
+    ds = p * (dp - (dp * p).sum(-1, keepdims=True))
+    dq = ds @ k / np.sqrt(D)
+    dk = np.swapaxes(ds, -1, -2) @ q / np.sqrt(D)
+    return o, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 50, 24), (2, 2, 300, 64), (1, 1, 64, 128)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_oracle_matches_fp64_math(shape, causal):
+    q, k, v, d_o = seeded(31, *shape)
+    o, lse = ol.fwd(q, k, v, causal)
+    dq, dk, dv = ol.bwd(q, k, v, d_o, causal)
+    ro, rlse, rdq, rdk, rdv = sdpa_f64(q, k, v, d_o, causal)
+    assert np.abs(o - ro).max() < 2e-6
+    assert np.abs(lse - rlse).max() < 5e-6
+    for a, b in ((dq, rdq), (dk, rdk), (dv, rdv)):
+        assert np.abs(a - b).max() < 2e-5
+
+
+def test_small_and_tiled_forward_agree():
+    q, k, v = seeded(32, 1, 2, 200, 64, with_do=False)
+    o1, l1 = ol.fwd(q, k, v, True, kernel=1)
+    o2, l2 = ol.fwd(q, k, v, True, kernel=2)
+    assert np.abs(o1 - o2).max() < 1e-6 and np.abs(l1 - l2).max() < 2e-6
+
+
+def test_backward_against_finite_differences():
+    # d/dx of L = sum(O * dO) by central differences in fp64 on a tiny case.
+    q, k, v, d_o = seeded(33, 1, 1, 6, 4)
+    _, _, rdq, rdk, rdv = sdpa_f64(q, k, v, d_o, True)
+    dq, dk, dv = ol.bwd(q, k, v, d_o, True)
+    eps = 1e-5
+
+    def loss(qq, kk, vv):
+        return (sdpa_f64(qq, kk, vv, d_o, True)[0] * d_o).sum()
+
+    for name, got in (("q", dq), ("k", dk), ("v", dv)):
+        base = {"q": q.astype(np.float64), "k": k.astype(np.float64), "v": v.astype(np.float64)}
+        num = np.zeros_like(base[name])
+        it = np.nditer(num, flags=["multi_index"])
+        for _ in it:
+            idx = it.multi_index
+            hi = {n: a.copy() for n, a in base.items()}
+            lo = {n: a.copy() for n, a in base.items()}
+            hi[name][idx] += eps
+            lo[name][idx] -= eps
+            num[idx] = (loss(hi["q"], hi["k"], hi["v"]) - loss(lo["q"], lo["k"], lo["v"])) / (2 * eps)
+        assert np.abs(got - num).max() < 1e-4, name
+
+
+def test_sequence_zero_and_bad_head_dim():
+    z = np.zeros((2, 2, 0, 8), np.float32)
+    o, lse = ol.fwd(z, z, z)
+    assert o.shape == (2, 2, 0, 8)
+    big = np.zeros((1, 1, 4, 129), np.float32)
+    with pytest.raises(ValueError):
+        ol.fwd(big, big, big)
+
+
+# ---------------------------------------------------------------- bf16 rule and the generator
+def test_bf16_rounding_rule():
+    x = np.array([1.0, 1.00390625, 1.01171875, -2.5, 3.1415927, 1e-40, 65504.0, np.inf, -np.inf], np.float32)
+    bits = ol.f32_to_bf16_bits(x)
+    assert np.array_equal(bits, synth.f32_to_bf16_bits(x))
+    # ties go to even: 1.00390625 = 0x3F808000 -> 0x3F80 ; 1.01171875 = 0x3F818000 -> 0x3F82
+    assert bits[1] == 0x3F80 and bits[2] == 0x3F82
+    assert bits[7] == 0x7F80 and bits[8] == 0xFF80
+    r = synth.bf16_bits_to_f32(bits)
+    assert np.all(np.abs(r[:5] - x[:5]) <= np.abs(x[:5]) * 2.0 ** -8)
+    rng = np.random.default_rng(0)
+    y = rng.standard_normal(100000).astype(np.float32)
+    assert np.array_equal(ol.f32_to_bf16_bits(y), synth.f32_to_bf16_bits(y))
+    import torch
+    assert np.array_equal(synth.round_bf16(y), torch.from_numpy(y).to(torch.bfloat16).float().numpy())
+
+
+def test_generator_is_counter_based():
+    full = synth.attention_inputs(5, 2, 3, 16, 8)
+    part = synth.attention_inputs(5, 2, 3, 16, 8, bh_begin=2, bh_end=5)
+    for a, b in zip(full, part):
+        assert np.array_equal(a[2:5], b)
+    q = full[0]
+    assert abs(q.mean()) < 0.1 and abs(q.std() - 1.0) < 0.1
+    assert not np.array_equal(full[0], full[1])
+    h = synth.attention_inputs(5, 2, 3, 16, 8, bf16=True, qk_scale=0.5)
+    assert np.array_equal(h[0], synth.round_bf16(h[0]))
