@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path: causal bf16 FlashAttention forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4|c3|c2]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" = one forward + one backward pass over the workload's batch of synthetic tensors.
+Default workload: B=4, H=16, S=8192, D=128 bf16 causal (the long-context configuration the
+headline metric is quoted on).  With N ranks the 64 (batch x head) slices are split contiguously,
+one process per GPU, no data-path collective (total work fixed: strong scaling); torch.distributed
+is used only for the barrier and the max-over-ranks of the device times.
+
+Prints ONE JSON line:
+  value        whole-job TFLOP/s with inputs resident in HBM (FLOPs: fwd 2*B*H*S^2*D, bwd 5*B*H*S^2*D,
+               the causal-halved FlashAttention convention), device time from CUDA events, max over ranks
+  e2e          the same metric through the package's public ops with HOST tensors: every step uploads
+               Q,K,V,dO from pinned memory and downloads O,dQ,dK,dV inside the timed region
+  roofline     the backward main kernel (dominant) against the measured dense-bf16 peak
+  cpu_baseline the CPU oracle timed on this box's host cores on a bounded sample (rank 0, N=1 only)
+--impl reference times the reference's algorithm on the host cores instead (the CPU oracle: the
+reference itself is Metal-only and cannot run here).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, S, D, qk_scale, description)
+    "c4": (4, 16, 8192, 128, 0.5, "causal bf16 attention fwd+bwd B4 H16 S8192 D128"),
+    "c3": (32, 12, 1024, 64, 1.0, "causal bf16 attention fwd+bwd B32 H12 S1024 D64"),
+    "c2": (16, 4, 256, 64, 1.0, "causal bf16 attention fwd+bwd B16 H4 S256 D64"),
+}
+METRIC = "causal attention fwd+bwd TFLOP/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of fa_bwd_sm100_kernel from an ncu capture
+# (see profiles/); None until one was taken for the workload.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {}
+
+
+def flops_fwd(bh, S, D):
+    return 2.0 * bh * S * S * D
+
+
+def flops_bwd(bh, S, D):
+    return 5.0 * bh * S * S * D
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16": p["bf16_tflops"], "bf16_sustained": p.get("bf16_tflops_sustained"), "hbm": p["hbm_gbs"],
+                "source": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.lines = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_oracle_rate(S, D, qk_scale, n_slices, seed):
+    """TFLOP/s of the CPU oracle (forward + composed backward) on `n_slices` head-slices of the workload."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    from irontensor_b200 import synth
+    q, k, v, d_o = [t.reshape(1, n_slices, S, D) for t in
+                    synth.attention_inputs(seed, 1, n_slices, S, D, bf16=True, qk_scale=qk_scale)]
+    ol.fwd(q[:, :1, :256], k[:, :1, :256], v[:, :1, :256])   # load the library, warm the thread pool
+    t0 = time.perf_counter()
+    ol.fwd(q, k, v, True)
+    ol.bwd(q, k, v, d_o, True)
+    dt = time.perf_counter() - t0
+    cores = ol.oracle().oracle_num_threads()
+    return (flops_fwd(n_slices, S, D) + flops_bwd(n_slices, S, D)) / dt / 1e12, dt, cores
+
+
+def run_reference(args, rank, world):
+    """The reference's algorithm on the host cores (the CPU oracle, all threads)."""
+    if rank != 0:
+        return
+    B, H, S, D, qs, desc = WORKLOADS[args.workload]
+    # bounded sample per step: head-slices of the workload at full sequence length
+    n_slices = 1 if S >= 4096 else min(B * H, 16)
+    rates = []
+    for i in range(args.warmup + args.steps):
+        r, dt, cores = cpu_oracle_rate(S, D, qs, n_slices, 0x1A7E5EED + 4 + i)
+        if i >= args.warmup:
+            rates.append((r, dt))
+    value = statistics.mean(r for r, _ in rates)
+    ms = statistics.mean(dt for _, dt in rates) * 1e3
+    sample = f"{n_slices} of {B * H} (batch x head) slices at full S={S}, fwd+bwd, per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "note": "reference is Metal-only; its algorithm restated in C++ (oracle/) runs on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from irontensor_b200 import Precision, Tensor, attention_backward_recompute, context, flash_attention, raw, synth
+    from irontensor_b200 import _lib
+    from irontensor_b200.sharding import shard_range
+
+    torch.cuda.set_device(local_rank)
+    ctx = context(local_rank)
+    B, H, S, D, qs, desc = WORKLOADS[args.workload]
+    BH = B * H
+    b0, b1 = shard_range(BH, world, rank)
+    nbh = b1 - b0
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- this rank's shard, generated on the device (seeded; same distribution as the parity tests' generator)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x1A7E5EED + 4 + 1000 * rank)
+    n = max(nbh, 1)
+
+    def mk(scale):
+        return (torch.randn((n, S, D), generator=gen, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
+
+    q, k, v, d_o = mk(qs), mk(qs), mk(1.0), mk(1.0)
+    o = torch.empty_like(q)
+    lse = torch.empty((n, S), dtype=torch.float32, device="cuda")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    ws_bytes = raw.bwd_workspace_bytes(_lib.IT_BF16, 1, n, S, D)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")   # > 126 MB L2
+
+    def step_device():
+        if nbh == 0:
+            return
+        raw.fwd(_lib.IT_BF16, 1, nbh, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                lse.data_ptr(), ctx=ctx)
+        raw.bwd(_lib.IT_BF16, 1, nbh, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws_bytes,
+                ctx=ctx)
+
+    ctx.enable_kernel_timing(True)
+    for _ in range(warmup):
+        step_device()
+    ctx.poll_status()
+
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    launches0 = ctx.launch_count()
+    barrier()
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    fwd_ms, bwd_ms = [], []
+    for i in range(steps):
+        flush.fill_(i & 0xFF)                 # evict the previous step's tensors from L2 (outside the event pair)
+        ev[i][0].record()
+        step_device()
+        ev[i][1].record()
+        if nbh:
+            fwd_ms.append(ctx.kernel_ms(0))   # waits for this step's kernels
+            bwd_ms.append(ctx.kernel_ms(1))
+    barrier()
+    clocks = sampler.stop()
+    launches = ctx.launch_count() - launches0
+    ctx.poll_status()
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    my_ms = sum(step_ms) / steps
+    ms_per_step = max_over_ranks(my_ms)
+    total_flops = flops_fwd(BH, S, D) + flops_bwd(BH, S, D)
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public ops with host tensors
+    hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, d_o))
+    ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
+    shape = [1, n, S, D]
+    tq, tk, tv, tdo = (Tensor.empty(shape, Precision.BF16) for _ in range(4))
+
+    def step_e2e():
+        tq.upload_from(hq), tk.upload_from(hk), tv.upload_from(hv), tdo.upload_from(hdo)
+        out = flash_attention(tq, tk, tv, True)
+        gq, gk, gv = attention_backward_recompute(tdo, tq, tk, tv, o=out, lse=out.lse)
+        out.download_to(ho), gq.download_to(hdq), gk.download_to(hdk), gv.download_to(hdv)
+
+    e2e_steps = steps
+    if nbh:
+        for _ in range(2):
+            step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    if nbh:
+        for _ in range(e2e_steps):
+            step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+    ctx.poll_status()
+    e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
+    nbytes = nbh * S * D * 2
+    if nbh:
+        assert torch.equal(ho.view(torch.int16), o[:nbh].cpu().view(torch.int16)), "e2e forward differs from the device-resident run"
+
+    if rank != 0:
+        return
+    peaks = measured_peaks()
+    bwd_avg_ms = statistics.mean(bwd_ms) if bwd_ms else float("nan")
+    fwd_avg_ms = statistics.mean(fwd_ms) if fwd_ms else float("nan")
+    ach = flops_bwd(nbh, S, D) / (bwd_avg_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": "fa_bwd_sm100_kernel", "achieved": ach, "peak": peaks["bf16"], "unit": "TFLOP/s",
+        "frac": ach / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload if world == 1 else None),
+        "peak_source": peaks["source"] + " (burst)", "avg_launch_ms": bwd_avg_ms,
+        "frac_of_sustained_peak": ach / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
+        "forward_kernel": {"kernel": "fa_fwd_sm100_kernel", "avg_launch_ms": fwd_avg_ms,
+                           "achieved": flops_fwd(nbh, S, D) / (fwd_avg_ms * 1e-3) / 1e12,
+                           "frac": flops_fwd(nbh, S, D) / (fwd_avg_ms * 1e-3) / 1e12 / peaks["bf16"]},
+    }
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "sharding": f"{BH} (batch x head) slices split contiguously over {world} GPU(s), no collective",
+                   "l2": "256 MB buffer written between timed steps; per-GPU tensors exceed L2 at N=1",
+                   "tflops_per_gpu": value / world, "frac_of_bf16_peak_per_gpu": value / world / peaks["bf16"]},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * nbytes,
+                "d2h_bytes_per_step": 4 * nbytes, "note": "bytes are rank 0's"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+    }
+    if world == 1 and not args.no_cpu:
+        n_slices = 4 if S >= 4096 else min(BH, 32)
+        r, dt, cores = cpu_oracle_rate(S, D, qs, n_slices, 0x1A7E5EED + 4)
+        line["cpu_baseline"] = {"value": r, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                "sample": f"{n_slices} of {BH} (batch x head) slices at full S={S}, fwd+bwd, {dt:.1f} s"}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world == 1:
+        # convenience: relaunch under torchrun, one rank per GPU
+        port = os.environ.get("MASTER_PORT", "29517")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", port, os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -118,6 +118,15 @@ it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* devi
 /* How many kernels this library has launched on this context since it was created. */
 it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out);
 
+/* Device-side timers around the two main kernels, the counterpart of the reference's
+ * OpCategory::FlashAttention timer (src/ops/flash_attention.rs:77, src/profile/timer.rs:27-36),
+ * which measures host encode time.  While enabled, each it_flash_attention_fwd / _bwd call
+ * records a CUDA event before and after its main kernel on the call's stream.
+ * it_ctx_kernel_ms waits for the most recent such pair and returns the time between them
+ * (which = 0: forward kernel, 1: backward main kernel). */
+it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable);
+it_status it_ctx_kernel_ms(it_ctx* ctx, int32_t which, float* ms);
+
 /* ---- self tests (no reference counterpart; they pin the hardware descriptors the kernels use) */
 
 /* One 128x128x128 bf16 MMA through the given operand path, result fp32 [128,128] row-major.

@@ -46,6 +46,8 @@ SIGNATURES = {
     "it_flash_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
     "it_attention_status_poll": [_vp, _vp, _c.POINTER(_i32)],
     "it_ctx_launch_count": [_vp, _c.POINTER(_c.c_uint64)],
+    "it_ctx_enable_kernel_timing": [_vp, _i32],
+    "it_ctx_kernel_ms": [_vp, _i32, _c.POINTER(_c.c_float)],
     "it_selftest_umma": [_vp, _vp, _i32, _vp, _vp, _vp],
     "it_selftest_wait_timeout": [_vp, _vp, _i32],
 }

@@ -48,6 +48,9 @@ struct it_ctx {
   int* d_status = nullptr;      // device status word written by kernels whose waits run out
   int* h_status = nullptr;      // pinned mirror
   EncodeTiledFn encode = nullptr;
+  bool timing = false;          // record events around the main kernels
+  cudaEvent_t ev[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};   // [fwd|bwd][start|stop]
+  bool ev_valid[2] = {false, false};
   std::atomic<uint64_t> launches{0};
 };
 struct it_stream {
@@ -150,7 +153,12 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causa
   p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
   const int n_pairs = (S + 255) / 256;
+  if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
   it::fa_fwd_sm100_kernel<D><<<static_cast<unsigned>(n_pairs) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  if (ctx->timing) {
+    IT_CUDA(cudaEventRecord(ctx->ev[0][1], s));
+    ctx->ev_valid[0] = true;
+  }
   ctx->launches += 1;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -216,7 +224,12 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causa
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const int n_kt = (S + 127) / 128;
+  if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
   it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  if (ctx->timing) {
+    IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
+    ctx->ev_valid[1] = true;
+  }
   const size_t n4 = n_dq / 4;
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
       dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale);
@@ -269,6 +282,9 @@ it_status it_ctx_destroy(it_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
+  for (int a = 0; a < 2; ++a)
+    for (int b = 0; b < 2; ++b)
+      if (ctx->ev[a][b] != nullptr) cudaEventDestroy(ctx->ev[a][b]);
   delete ctx;
   return IT_OK;
 }
@@ -494,6 +510,26 @@ it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* devi
     IT_CUDA(cudaStreamSynchronize(stream->s));
     return fail(IT_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (device status %d)", *device_status);
   }
+  return IT_OK;
+}
+
+it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable) {
+  if (ctx == nullptr) return fail(IT_ERR_INVALID_ARG, "null context");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  if (enable && ctx->ev[0][0] == nullptr) {
+    for (int a = 0; a < 2; ++a)
+      for (int b = 0; b < 2; ++b) IT_CUDA(cudaEventCreate(&ctx->ev[a][b]));
+  }
+  ctx->timing = enable != 0;
+  return IT_OK;
+}
+
+it_status it_ctx_kernel_ms(it_ctx* ctx, int32_t which, float* ms) {
+  if (ctx == nullptr || ms == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  if (which < 0 || which > 1) return fail(IT_ERR_INVALID_ARG, "which must be 0 (forward) or 1 (backward)");
+  if (!ctx->ev_valid[which]) return fail(IT_ERR_INVALID_ARG, "no timed launch of that kernel yet");
+  IT_CUDA(cudaEventSynchronize(ctx->ev[which][1]));
+  IT_CUDA(cudaEventElapsedTime(ms, ctx->ev[which][0], ctx->ev[which][1]));
   return IT_OK;
 }
 

@@ -109,12 +109,12 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                   make_idesc(128, 128, false, true), kk > 0);
         } else if (VARIANT == 2) {
           umma_ss(tmem_base, sdesc_advance(make_sdesc(a_addr, 16, 1024), koff),
-                  sdesc_advance(make_sdesc(b_addr, BLOCK_BYTES, 1024), kk * 2048), make_idesc(128, 128, false, true),
-                  kk > 0);
+                  sdesc_advance(make_sdesc(b_addr, BLOCK_BYTES, 1024), kk * 2048),
+                  make_idesc(128, 128, false, true), kk > 0);
         } else {
           umma_ss(tmem_base, sdesc_advance(make_sdesc(a_addr, BLOCK_BYTES, 1024), kk * 2048),
-                  sdesc_advance(make_sdesc(b_addr, BLOCK_BYTES, 1024), kk * 2048), make_idesc(128, 128, true, true),
-                  kk > 0);
+                  sdesc_advance(make_sdesc(b_addr, BLOCK_BYTES, 1024), kk * 2048),
+                  make_idesc(128, 128, true, true), kk > 0);
         }
       }
       umma_commit(mma_done);

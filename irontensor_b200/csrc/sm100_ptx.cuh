@@ -157,6 +157,8 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
 // ---------------------------------------------------------------- tcgen05.mma (bf16 x bf16 -> fp32)
 // Instruction descriptor for kind::f16: D fp32, A/B bf16; *_mn selects MN-major (the M or N index
 // is the contiguous one in shared memory) instead of K-major.
+// A and B must have the same element type: an fp16 A with a bf16 B is rejected by the hardware
+// as an illegal instruction, so P and dS go to the tensor core as bf16 like Q, K, V and dO.
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool a_mn, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) |
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);

@@ -68,6 +68,15 @@ class _Context:
         _lib.check(self.lib.it_ctx_launch_count(self.handle, ctypes.byref(n)))
         return n.value
 
+    def enable_kernel_timing(self, on=True):
+        _lib.check(self.lib.it_ctx_enable_kernel_timing(self.handle, int(on)))
+
+    def kernel_ms(self, which):
+        """Device time of the most recent forward (0) or backward-main (1) kernel."""
+        ms = ctypes.c_float()
+        _lib.check(self.lib.it_ctx_kernel_ms(self.handle, which, ctypes.byref(ms)))
+        return ms.value
+
     def poll_status(self):
         """Drains the current stream; raises ITError(IT_ERR_TIMEOUT) if a kernel's wait ran out."""
         st = ctypes.c_int32()
@@ -185,6 +194,29 @@ class Tensor:
     def from_f32_as_bf16(data, shape):
         return Tensor.from_bf16_slice(synth.f32_to_bf16_bits(np.asarray(data, dtype=np.float32).reshape(-1)), shape)
 
+    @staticmethod
+    def empty(shape, precision=Precision.FP32):
+        """Uninitialised storage, for outputs a kernel overwrites completely."""
+        torch = _torch()
+        dt = torch.float32 if precision is Precision.FP32 else torch.bfloat16
+        n = int(np.prod(shape)) if len(shape) else 1
+        return Tensor(torch.empty(max(n, 1), dtype=dt, device="cuda")[:n], shape, precision)
+
+    # -- explicit, stream-ordered copies to and from page-locked host memory
+    def upload_from(self, host):
+        """Asynchronous host -> device copy of a pinned torch tensor with the same byte size."""
+        c = context()
+        assert host.is_pinned() and host.numel() * host.element_size() == self.byte_size()
+        _lib.check(c.lib.it_buf_upload(c.handle, c.stream(), self.data_ptr(), host.data_ptr(), self.byte_size()))
+        return self
+
+    def download_to(self, host):
+        """Asynchronous device -> host copy into a pinned torch tensor with the same byte size."""
+        c = context()
+        assert host.is_pinned() and host.numel() * host.element_size() == self.byte_size()
+        _lib.check(c.lib.it_buf_download(c.handle, c.stream(), host.data_ptr(), self.data_ptr(), self.byte_size()))
+        return host
+
     # -- accessors
     def shape(self):
         return list(self._shape)
@@ -297,10 +329,12 @@ def flash_attention(q, k, v, causal):
     assert qs == vs, "Q and V must have same shape"
     B, H, S, D = qs
     assert D <= 128, "head_dim must be <= 128"
-    out = Tensor.zeros([B, H, S, D], p)
-    out.lse = Tensor.zeros([B, H, S], Precision.FP32)
     if S == 0 or B * H == 0:
+        out = Tensor.zeros([B, H, S, D], p)
+        out.lse = Tensor.zeros([B, H, S], Precision.FP32)
         return out
+    out = Tensor.empty([B, H, S, D], p)     # the kernel writes every element
+    out.lse = Tensor.empty([B, H, S], Precision.FP32)
     raw.fwd(_dtype_code(p), B, H, S, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
             out.lse.data_ptr())
     return out
@@ -346,9 +380,9 @@ def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=
     B, H, S, D = q.shape()
     for t in (grad_output, k, v):
         assert t.shape() == [B, H, S, D], "shape mismatch"
-    dq, dk, dv = Tensor.zeros([B, H, S, D], p), Tensor.zeros([B, H, S, D], p), Tensor.zeros([B, H, S, D], p)
     if S == 0 or B * H == 0:
-        return dq, dk, dv
+        return Tensor.zeros([B, H, S, D], p), Tensor.zeros([B, H, S, D], p), Tensor.zeros([B, H, S, D], p)
+    dq, dk, dv = Tensor.empty([B, H, S, D], p), Tensor.empty([B, H, S, D], p), Tensor.empty([B, H, S, D], p)
     if o is None or lse is None:
         o = flash_attention(q, k, v, causal)
         lse = o.lse
