@@ -78,7 +78,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
@@ -168,6 +168,9 @@ def run_ours(args, rank, world, local_rank):
     ctx = context(local_rank)
     B, H, S, D, qs, desc = WORKLOADS[args.workload]
     BH = B * H
+    if args.slices:
+        BH = min(BH, args.slices)
+        desc += f" (reduced to {BH} slices)"
     b0, b1 = shard_range(BH, world, rank)
     nbh = b1 - b0
     steps, warmup = args.steps, max(args.warmup, 3)
@@ -219,6 +222,7 @@ def run_ours(args, rank, world, local_rank):
     launches0 = ctx.launch_count()
     barrier()
     sampler.start()
+    time.sleep(0.1)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     fwd_ms, bwd_ms = [], []
     for i in range(steps):
@@ -230,7 +234,6 @@ def run_ours(args, rank, world, local_rank):
             fwd_ms.append(ctx.kernel_ms(0))   # waits for this step's kernels
             bwd_ms.append(ctx.kernel_ms(1))
     barrier()
-    clocks = sampler.stop()
     launches = ctx.launch_count() - launches0
     ctx.poll_status()
     step_ms = [a.elapsed_time(b) for a, b in ev]
@@ -240,6 +243,15 @@ def run_ours(args, rank, world, local_rank):
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public ops with host tensors
+    if args.no_e2e:
+        clocks = sampler.stop()
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+                              "warmup": warmup, "ms_per_step": ms_per_step, "config": {"workload": desc},
+                              "kernel_ms": {"fwd": statistics.mean(fwd_ms), "bwd": statistics.mean(bwd_ms)},
+                              "gpu_launches": int(launches), "clocks": clocks, "note": "profiling run: no e2e / cpu legs"}),
+                  flush=True)
+        return
     hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, d_o))
     ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
     shape = [1, n, S, D]
@@ -264,6 +276,7 @@ def run_ours(args, rank, world, local_rank):
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+    clocks = sampler.stop()      # sampled across the device-resident and the end-to-end timed regions
     ctx.poll_status()
     e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
     nbytes = nbh * S * D * 2
@@ -314,6 +327,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
+    ap.add_argument("--slices", type=int, default=0,
+                    help="use only this many (batch x head) slices of the workload (small profiling cases)")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
