@@ -40,9 +40,10 @@ WORKLOADS = {
 }
 METRIC = "causal attention fwd+bwd TFLOP/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of fa_bwd_sm100_kernel from an ncu capture
-# (see profiles/); None until one was taken for the workload.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of fa_bwd_sm100_kernel from an ncu capture:
+# profiles/fa_bwd_sm100_c4_32slices_ncu.md measured 1.968 GB + 1.013 GB on 32 of the 64 slices; traffic
+# grows in proportion to the slices a launch processes, so the full launch is twice that.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c4": 2 * (1.967934e9 + 1.012733e9)}
 
 
 def flops_fwd(bh, S, D):
