@@ -109,6 +109,32 @@ it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype,
                                  const void* v, const void* o, const void* d_o, const float* lse, void* dq,
                                  void* dk, void* dv, void* workspace, size_t workspace_bytes);
 
+/* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
+ * there every op allocates its own buffers, src/tensor.rs:63-84.)
+ *
+ * Who needs it: a host that runs inside someone else's CUDA context and was handed only tensor
+ * pointers and a stream -- for instance a plugin called from a real-time or sandboxed process
+ * whose policy forbids cudaMalloc after start-up, or code running while another component owns
+ * the allocator and any allocation could stall or fail.  Such a caller has nowhere to take
+ * it_flash_attention_bwd's workspace from.  Here the scratch is a fixed array of
+ * IT_NOALLOC_SCRATCH_BYTES that is part of the library image: every GPU that loads the library
+ * holds that much memory until the process exits, whether or not this call is ever made.
+ *
+ * Same arguments, results and dispatch as it_flash_attention_bwd, minus the workspace.  Differences:
+ *   - the shape is refused with IT_ERR_UNSUPPORTED_SHAPE when its scratch need
+ *     (it_flash_attention_bwd_workspace_bytes) exceeds IT_NOALLOC_SCRATCH_BYTES;
+ *   - this call makes no cudaMalloc / cudaFree and calls nothing that allocates device memory;
+ *   - the first call on each device looks up the array's device address (a symbol lookup, once per
+ *     device): make that first call outside any stream capture;
+ *   - all calls on one GPU share the one array, and it keeps the previous call's contents; the call
+ *     clears what has to start from zero itself.  Two calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering between them) race on it: order them. */
+#define IT_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
+it_status it_flash_attention_bwd_noalloc(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch,
+                                         int32_t heads, int32_t seq, int32_t head_dim, int32_t causal,
+                                         const void* q, const void* k, const void* v, const void* o,
+                                         const void* d_o, const float* lse, void* dq, void* dk, void* dv);
+
 /* Kernels never spin without bound: a wait that runs out (about one second) records a code in a
  * device status word and the kernel winds down.  This call drains `stream`, returns the word in
  * *device_status (0 = clean) and clears it.  Returns IT_ERR_TIMEOUT when the word was non-zero.

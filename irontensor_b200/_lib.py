@@ -15,6 +15,7 @@ IT_ERR_CUDA = -5
 IT_ERR_TIMEOUT = -6
 IT_F32 = 0
 IT_BF16 = 1
+IT_NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024
 
 _c = ctypes
 _vp = _c.c_void_p
@@ -44,6 +45,7 @@ SIGNATURES = {
     "it_flash_attention_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "it_flash_attention_bwd_workspace_bytes": [_c.c_int, _i32, _i32, _i32, _i32, _c.POINTER(_c.c_size_t)],
     "it_flash_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
+    "it_flash_attention_bwd_noalloc": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9,
     "it_attention_status_poll": [_vp, _vp, _c.POINTER(_i32)],
     "it_ctx_launch_count": [_vp, _c.POINTER(_c.c_uint64)],
     "it_ctx_enable_kernel_timing": [_vp, _i32],

@@ -11,6 +11,7 @@
 #include <cstring>
 #include <atomic>
 #include <cmath>
+#include <mutex>
 #include <new>
 
 #include "fa_bwd_sm100.cuh"
@@ -497,6 +498,44 @@ it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype,
     launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta);
   IT_CUDA(cudaGetLastError());
   return IT_OK;
+}
+
+// Scratch for it_flash_attention_bwd_noalloc: part of the module image on every GPU that loads it.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[IT_NOALLOC_SCRATCH_BYTES];
+static std::mutex g_noalloc_mutex;
+static void* g_noalloc_ptr[64] = {};   // device address of the array, per device ordinal
+
+it_status it_flash_attention_bwd_noalloc(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H,
+                                         int32_t S, int32_t D, int32_t causal, const void* q, const void* k,
+                                         const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+                                         void* dk, void* dv) {
+  it_status st = check_common(ctx, stream, dtype, B, H, S, D);
+  if (st != IT_OK) return st;
+  if (S == 0 || B * H == 0) return IT_OK;
+  const size_t need = bwd_workspace_layout(dtype, static_cast<int64_t>(B) * H, S, D).total;
+  if (need > IT_NOALLOC_SCRATCH_BYTES)
+    return fail(IT_ERR_UNSUPPORTED_SHAPE,
+                "this shape needs %zu bytes of scratch; the built-in scratch of the allocation-free backward holds %u",
+                need, static_cast<unsigned>(IT_NOALLOC_SCRATCH_BYTES));
+  if (ctx->device < 0 || ctx->device >= 64) return fail(IT_ERR_INVALID_ARG, "device ordinal %d out of range", ctx->device);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[ctx->device] == nullptr) {
+      // once per device, with that device current
+      IT_CUDA(cudaSetDevice(ctx->device));
+      void* p = nullptr;
+      IT_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+      if (p == nullptr) return fail(IT_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+      g_noalloc_ptr[ctx->device] = p;
+    }
+    scratch = g_noalloc_ptr[ctx->device];
+  }
+  // The regular entry point clears the dQ accumulator and rewrites the per-row arrays on every call,
+  // so nothing left in the array by an earlier call is read.
+  return it_flash_attention_bwd(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, scratch,
+                                IT_NOALLOC_SCRATCH_BYTES);
 }
 
 it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* device_status) {
