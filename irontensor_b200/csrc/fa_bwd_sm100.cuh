@@ -14,11 +14,19 @@
 //                                dV += P^T dO         dK += dS^T Q         dQ_i = dS K
 //                              P^T feeds its MMA straight from TMEM; dS^T goes to shared memory once
 //                              and is read K-major by the dK MMA and M-major by the dQ MMA.  dQ
-//                              tiles are added into an fp32 workspace with vector atomics.
+//                              tiles go TMEM -> registers -> swizzled shared memory -> TMA
+//                              reduce-add into an fp32 workspace (whole-line reductions in L2;
+//                              per-thread 16-byte atomics cost a third of the kernel's time).
 //   3. fa_bwd_finish_kernel  : dQ = bf16(workspace * 1/sqrt(D)).
 // Warp roles in (2): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocation,
-// warps 4-7 softmax/dS math (one thread per key row), warps 8-11 dQ drain.
-// TMEM columns (512): S^T/P^T [0,128)  dP^T and dQ (aliased) [128,256)  dV [256,256+D)  dK [384,384+D).
+// warps 4-7 and 8-11 two math groups (P^T, dS^T; a thread owns one key row and one half of the 128
+// query columns), warps 12-15 dQ drain.  Per query tile the tensor core sees, in order:
+//   dP^T(n) | [P^T(n) ready] dV(n), S^T(n+1) | [dS^T(n) ready] dQ(n), dK(n) | [dQ(n) drained] dP^T(n+1) ...
+// so the math groups work on dS^T(n) while dV(n) and S^T(n+1) run, and on P^T(n+1) while dQ(n), dK(n)
+// run; dQ is issued before dK so that its drain overlaps the dK MMA.
+// TMEM columns (512): S^T [0,128) with P^T written over it (queries 0-63 packed in [0,32), 64-127 in
+// [64,96): each math group overwrites only columns it has already read), dP^T and dQ (aliased) [128,256),
+// dV [256,256+D), dK [384,384+D).
 #pragma once
 #include "sm100_ptx.cuh"
 
@@ -34,15 +42,16 @@ struct BwdTraits {
   static constexpr int SMEM_K = 0;
   static constexpr int SMEM_V = SMEM_K + TILE_BYTES;
   static constexpr int SMEM_Q = SMEM_V + TILE_BYTES;        // 2 stages
-  static constexpr int SMEM_DO = SMEM_Q + 2 * TILE_BYTES;   // 2 stages
-  static constexpr int SMEM_DS = SMEM_DO + 2 * TILE_BYTES;  // [2 blocks][128 keys][64 q] bf16
-  static constexpr int SMEM_LSE = SMEM_DS + 2 * BLOCK_BYTES;   // [2 stages][128] fp32
+  static constexpr int SMEM_DO = SMEM_Q + 2 * TILE_BYTES;   // 1 stage: dO(n) is free again well before dP^T(n+1)
+  static constexpr int SMEM_DS = SMEM_DO + TILE_BYTES;      // [2 blocks][128 keys][64 q] bf16
+  static constexpr int SMEM_DQS = SMEM_DS + 2 * BLOCK_BYTES;   // dQ staging: [2][128 rows][32 fp32], 128B swizzle
+  static constexpr int SMEM_LSE = SMEM_DQS + 2 * BLOCK_BYTES;  // [2 stages][128] fp32
   static constexpr int SMEM_DELTA = SMEM_LSE + 2 * 512;        // [2 stages][128] fp32
   static constexpr int SMEM_BAR = SMEM_DELTA + 2 * 512;
-  static constexpr int NUM_BARS = 16;
+  static constexpr int NUM_BARS = 20;
   static constexpr int SMEM_MISC = SMEM_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = SMEM_MISC + 16;
-  static constexpr int THREADS = 384;
+  static constexpr int THREADS = 512;
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DQ = 128, COL_DV = 256, COL_DK = 384;
 };
@@ -121,10 +130,10 @@ __global__ void fa_bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bf
 
 // ------------------------------------------------------------------ (2) main kernel
 template <int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                    const BwdParams prm) {
+                    const __grid_constant__ CUtensorMap tmap_dq, const BwdParams prm) {
   using T = BwdTraits<D>;
   using namespace ptx;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -133,8 +142,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* kv_full = bars + 0;
   uint64_t* q_full = bars + 1;     // [2]
   uint64_t* q_empty = bars + 3;    // [2]
-  uint64_t* do_full = bars + 5;    // [2]
-  uint64_t* do_empty = bars + 7;   // [2]
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_empty = bars + 7;
   uint64_t* st_full = bars + 9;
   uint64_t* dpt_full = bars + 10;
   uint64_t* p_full = bars + 11;
@@ -142,6 +151,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* dq_full = bars + 13;
   uint64_t* dq_empty = bars + 14;
   uint64_t* dkv_done = bars + 15;
+  uint64_t* dqs_free = bars + 16;  // [2] staging buffer may be rewritten
+  uint64_t* dqs_full = bars + 18;  // [2] staging buffer holds a chunk
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + T::SMEM_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::SMEM_MISC + 4);
 
@@ -149,9 +160,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int lane = threadIdx.x & 31;
   const int S = prm.S;
   const int n_q_tiles = (S + T::BN - 1) / T::BN;
-  // Key tile 0 sees every query tile (most work under the causal mask): schedule it first.
-  const int kt = static_cast<int>(blockIdx.x) / prm.BH;
-  const int bh = static_cast<int>(blockIdx.x) % prm.BH;
+  // Head-major order: the CTAs resident at one time belong to two or three (batch, head) slices, so
+  // their Q/dO streams and the fp32 dQ accumulator they add into stay in L2.  Within a slice key
+  // tile 0 comes first: under the causal mask it sees every query tile and has the most work.
+  const int n_k_tiles = (S + T::BM - 1) / T::BM;
+  const int bh = static_cast<int>(blockIdx.x) / n_k_tiles;
+  const int kt = static_cast<int>(blockIdx.x) % n_k_tiles;
   const int i0 = prm.causal ? kt : 0;
   const int n_iter = n_q_tiles - i0;
 
@@ -168,16 +182,20 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
-      mbar_init(&do_full[i], 1);
-      mbar_init(&do_empty[i], 1);
     }
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
     mbar_init(st_full, 1);
     mbar_init(dpt_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(ds_full, 128);
+    mbar_init(p_full, 256);
+    mbar_init(ds_full, 256);
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 128);
     mbar_init(dkv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&dqs_free[i], 1);
+      mbar_init(&dqs_full[i], 128);
+    }
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -199,6 +217,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
         prefetch_tensormap(&tmap_do);
+        prefetch_tensormap(&tmap_dq);
         mbar_arrive_expect_tx(kv_full, 2 * T::TILE_BYTES);
         for (int b = 0; b < T::NBLK; ++b) {
           tma_load_3d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, bh);
@@ -224,11 +243,10 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                   smem_addr(smem + T::SMEM_DELTA + st * 512)),
               "l"(reinterpret_cast<uint64_t>(prm.delta_pad + row0)), "r"(smem_addr(&q_full[st]))
               : "memory");
-          if (!mbar_wait(&do_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
-          mbar_arrive_expect_tx(&do_full[st], T::TILE_BYTES);
+          if (!mbar_wait(do_empty, (n & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
+          mbar_arrive_expect_tx(do_full, T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
-            tma_load_3d(smem + T::SMEM_DO + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_do, &do_full[st], b * 64,
-                        qi * T::BN, bh);
+            tma_load_3d(smem + T::SMEM_DO + b * T::BLOCK_BYTES, &tmap_do, do_full, b * 64, qi * T::BN, bh);
         }
       }
     } else if (warp == 1) {
@@ -252,21 +270,21 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     IDESC_SS, kk > 0);
           umma_commit(st_full);
         };
-        auto issue_dpt = [&](int st) {   // dP^T = V * dO^T
+        auto issue_dpt = [&]() {   // dP^T = V * dO^T
           const uint64_t da = make_sdesc(v_addr, 16, 1024);
-          const uint64_t db = make_sdesc(do_addr + st * T::TILE_BYTES, 16, 1024);
+          const uint64_t db = make_sdesc(do_addr, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
             umma_ss(tmem_base + T::COL_DPT, sdesc_advance(da, kmajor_off(kk)), sdesc_advance(db, kmajor_off(kk)),
                     IDESC_SS, kk > 0);
           umma_commit(dpt_full);
         };
-        auto issue_dv = [&](int st, bool first) {   // dV += P^T * dO   (A from TMEM, B = dO N-major)
-          const uint64_t db = make_sdesc(do_addr + st * T::TILE_BYTES, T::BLOCK_BYTES, 1024);
+        auto issue_dv = [&](bool first) {   // dV += P^T * dO   (A from TMEM, B = dO N-major)
+          const uint64_t db = make_sdesc(do_addr, T::BLOCK_BYTES, 1024);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ts(tmem_base + T::COL_DV, tmem_base + T::COL_ST + kk * 8, sdesc_advance(db, kk * 2048), IDESC_ND,
-                    (!first || kk > 0) ? 1u : 0u);
+            umma_ts(tmem_base + T::COL_DV, tmem_base + T::COL_ST + (kk >> 2) * 64 + (kk & 3) * 8,
+                    sdesc_advance(db, kk * 2048), IDESC_ND, (!first || kk > 0) ? 1u : 0u);
         };
         auto issue_dk = [&](int st, bool first) {   // dK += dS^T * Q   (A = dS^T K-major, B = Q N-major)
           const uint64_t da = make_sdesc(ds_addr, 16, 1024);
@@ -293,19 +311,19 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int n = 0; n < n_iter && ok; ++n) {
           const int st = n & 1;
           const uint32_t ph = (n >> 1) & 1;
-          ok = mbar_wait(&do_full[st], ph, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+          ok = mbar_wait(do_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
           if (!ok) break;
           if (n > 0) {   // dQ(n-1) must have left TMEM before dP^T(n) overwrites those columns
             ok = mbar_wait(dq_empty, (n - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
             if (!ok) break;
           }
           tc_fence_after();
-          issue_dpt(st);
+          issue_dpt();
           ok = mbar_wait(p_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
-          issue_dv(st, n == 0);
-          umma_commit(&do_empty[st]);
+          issue_dv(n == 0);
+          umma_commit(do_empty);
           if (n + 1 < n_iter) {
             const int st_n = (n + 1) & 1;
             const uint32_t ph_n = ((n + 1) >> 1) & 1;
@@ -317,55 +335,73 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           ok = mbar_wait(ds_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
-          issue_dk(st, n == 0);
           issue_dq();
-          umma_commit(&q_empty[st]);
           umma_commit(dq_full);
+          issue_dk(st, n == 0);
+          umma_commit(&q_empty[st]);
         }
         if (ok) umma_commit(dkv_done);
       }
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp >= 4 && warp < 12) {
       // ------------------------------------------------------------ P^T and dS^T math, dK/dV epilogue
+      const int half = (warp - 4) >> 2;                 // which 64 of the 128 query columns
       const int lane_base = (warp & 3) * 32;
       const int k_local = lane_base + lane;
       const int k_row = kt * T::BM + k_local;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
+      const uint32_t t_st = t_lane + T::COL_ST + half * 64;
+      const uint32_t t_dpt = t_lane + T::COL_DPT + half * 64;
       const float sl2 = prm.scale_log2;
-      uint8_t* ds_row = smem + T::SMEM_DS + k_local * 128;
+      uint8_t* ds_row = smem + T::SMEM_DS + half * T::BLOCK_BYTES + k_local * 128;
       const int swz = k_local & 7;
       bool ok = true;
-      uint32_t r[32];
-      uint32_t p_keep[64];   // P^T row, packed bf16, kept between the two phases
+      uint32_t ra[16], rb[16];
+      uint32_t p_keep[32];   // this thread's 64 P^T values, packed bf16, kept between the two phases
       for (int n = 0; n < n_iter; ++n) {
         const int st = n & 1;
         const int qi = i0 + n;
         const bool diag = prm.causal && (qi == kt);
-        const float* lse_s = reinterpret_cast<const float*>(smem + T::SMEM_LSE + st * 512);
-        const float* dl_s = reinterpret_cast<const float*>(smem + T::SMEM_DELTA + st * 512);
+        const float* lse_s = reinterpret_cast<const float*>(smem + T::SMEM_LSE + st * 512) + half * 64;
+        const float* dl_s = reinterpret_cast<const float*>(smem + T::SMEM_DELTA + st * 512) + half * 64;
         // lse/delta for this query tile ride on the Q barrier
         ok = mbar_wait(&q_full[st], (n >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
         if (ok) ok = mbar_wait(st_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        // phase A: P^T = 2^(S^T * scale*log2e - LSE*log2e)
+        // phase A: P^T = 2^(S^T * scale*log2e - LSE*log2e); the next 16 columns load while these are computed
+        auto phase_a = [&](const uint32_t (&r)[16], int c) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_x32(t_lane + T::COL_ST + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 l2 = *reinterpret_cast<const float2*>(lse_s + c * 32 + i);
-            float p0 = ex2(fmaf(__uint_as_float(r[i]), sl2, -l2.x));
-            float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sl2, -l2.y));
+          for (int i = 0; i < 16; i += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c * 16 + i);
+            float p0 = ex2(fmaf(__uint_as_float(r[i + 0]), sl2, -l4.x));
+            float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sl2, -l4.y));
+            float p2 = ex2(fmaf(__uint_as_float(r[i + 2]), sl2, -l4.z));
+            float p3 = ex2(fmaf(__uint_as_float(r[i + 3]), sl2, -l4.w));
             if (diag) {   // key after the query: masked
-              if (k_local > c * 32 + i) p0 = 0.f;
-              if (k_local > c * 32 + i + 1) p1 = 0.f;
+              const int qc = half * 64 + c * 16 + i;
+              if (k_local > qc + 0) p0 = 0.f;
+              if (k_local > qc + 1) p1 = 0.f;
+              if (k_local > qc + 2) p2 = 0.f;
+              if (k_local > qc + 3) p3 = 0.f;
             }
-            p_keep[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+            p_keep[c * 8 + (i >> 1)] = pack_bf16(p0, p1);
+            p_keep[c * 8 + (i >> 1) + 1] = pack_bf16(p2, p3);
           }
-          tmem_st_x16(t_lane + T::COL_ST + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&p_keep[c * 16]));
-        }
+        };
+        tmem_ld_x16(t_st, ra);
+        tmem_wait_ld();
+        tmem_ld_x16(t_st + 16, rb);
+        phase_a(ra, 0);
+        tmem_wait_ld();
+        tmem_ld_x16(t_st + 32, ra);
+        phase_a(rb, 1);
+        tmem_wait_ld();
+        tmem_ld_x16(t_st + 48, rb);
+        phase_a(ra, 2);
+        tmem_wait_ld();
+        phase_a(rb, 3);
+        tmem_st_x32(t_st, p_keep);   // 64 queries -> 32 packed columns at the start of this group's own range
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full);
@@ -374,28 +410,33 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        auto phase_b = [&](const uint32_t (&r)[16], int c) {
+          uint32_t dsp[8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_x32(t_lane + T::COL_DPT + c * 32, r);
-          tmem_wait_ld();
-          uint32_t dsp[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 dl = *reinterpret_cast<const float2*>(dl_s + c * 32 + i);
-            const uint32_t pp = p_keep[c * 16 + (i >> 1)];
-            const float p0 = __uint_as_float(pp << 16);
-            const float p1 = __uint_as_float(pp & 0xFFFF0000u);
-            dsp[i >> 1] = pack_bf16(p0 * (__uint_as_float(r[i]) - dl.x), p1 * (__uint_as_float(r[i + 1]) - dl.y));
+          for (int i = 0; i < 16; i += 4) {
+            const float4 d4 = *reinterpret_cast<const float4*>(dl_s + c * 16 + i);
+            const uint32_t pa = p_keep[c * 8 + (i >> 1)], pb = p_keep[c * 8 + (i >> 1) + 1];
+            const float p0 = __uint_as_float(pa << 16), p1 = __uint_as_float(pa & 0xFFFF0000u);
+            const float p2 = __uint_as_float(pb << 16), p3 = __uint_as_float(pb & 0xFFFF0000u);
+            dsp[i >> 1] = pack_bf16(p0 * (__uint_as_float(r[i + 0]) - d4.x), p1 * (__uint_as_float(r[i + 1]) - d4.y));
+            dsp[(i >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(r[i + 2]) - d4.z), p3 * (__uint_as_float(r[i + 3]) - d4.w));
           }
-          // 32 query columns = four 16-byte chunks of this key row, in 64-column block (c >> 1)
-          uint8_t* blk = ds_row + (c >> 1) * T::BLOCK_BYTES;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            const int chunk = (c & 1) * 4 + ch;
-            *reinterpret_cast<uint4*>(blk + ((chunk ^ swz) << 4)) =
-                make_uint4(dsp[ch * 4 + 0], dsp[ch * 4 + 1], dsp[ch * 4 + 2], dsp[ch * 4 + 3]);
-          }
-        }
+          // 16 query columns = two 16-byte chunks of this key row
+          *reinterpret_cast<uint4*>(ds_row + (((2 * c) ^ swz) << 4)) = make_uint4(dsp[0], dsp[1], dsp[2], dsp[3]);
+          *reinterpret_cast<uint4*>(ds_row + (((2 * c + 1) ^ swz) << 4)) = make_uint4(dsp[4], dsp[5], dsp[6], dsp[7]);
+        };
+        tmem_ld_x16(t_dpt, ra);
+        tmem_wait_ld();
+        tmem_ld_x16(t_dpt + 16, rb);
+        phase_b(ra, 0);
+        tmem_wait_ld();
+        tmem_ld_x16(t_dpt + 32, ra);
+        phase_b(rb, 1);
+        tmem_wait_ld();
+        tmem_ld_x16(t_dpt + 48, rb);
+        phase_b(ra, 2);
+        tmem_wait_ld();
+        phase_b(rb, 3);
         tc_fence_before();
         fence_proxy_async_smem();
         mbar_arrive(ds_full);
@@ -405,62 +446,86 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
+        // each math group writes one half of the head dimension of its key row's dV and dK
         tc_fence_after();
-        __nv_bfloat16* dv_row = prm.dv + (static_cast<size_t>(bh) * S + k_row) * D;
-        __nv_bfloat16* dk_row = prm.dk + (static_cast<size_t>(bh) * S + k_row) * D;
+        constexpr int HC = D / 2;
+        __nv_bfloat16* dv_row = prm.dv + (static_cast<size_t>(bh) * S + k_row) * D + half * HC;
+        __nv_bfloat16* dk_row = prm.dk + (static_cast<size_t>(bh) * S + k_row) * D + half * HC;
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
-          const uint32_t col = which ? T::COL_DK : T::COL_DV;
+          const uint32_t col = (which ? T::COL_DK : T::COL_DV) + half * HC;
           const float f = which ? prm.scale : 1.0f;
           __nv_bfloat16* orow = which ? dk_row : dv_row;
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            tmem_ld_x32(t_lane + col + c * 32, r);
+          for (int c = 0; c < HC / 16; ++c) {
+            tmem_ld_x16(t_lane + col + c * 16, ra);
             tmem_wait_ld();
             if (k_row < S) {
 #pragma unroll
-              for (int v4 = 0; v4 < 4; ++v4) {
+              for (int v4 = 0; v4 < 2; ++v4) {
                 uint4 w;
-                w.x = pack_bf16(__uint_as_float(r[v4 * 8 + 0]) * f, __uint_as_float(r[v4 * 8 + 1]) * f);
-                w.y = pack_bf16(__uint_as_float(r[v4 * 8 + 2]) * f, __uint_as_float(r[v4 * 8 + 3]) * f);
-                w.z = pack_bf16(__uint_as_float(r[v4 * 8 + 4]) * f, __uint_as_float(r[v4 * 8 + 5]) * f);
-                w.w = pack_bf16(__uint_as_float(r[v4 * 8 + 6]) * f, __uint_as_float(r[v4 * 8 + 7]) * f);
-                *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = w;
+                w.x = pack_bf16(__uint_as_float(ra[v4 * 8 + 0]) * f, __uint_as_float(ra[v4 * 8 + 1]) * f);
+                w.y = pack_bf16(__uint_as_float(ra[v4 * 8 + 2]) * f, __uint_as_float(ra[v4 * 8 + 3]) * f);
+                w.z = pack_bf16(__uint_as_float(ra[v4 * 8 + 4]) * f, __uint_as_float(ra[v4 * 8 + 5]) * f);
+                w.w = pack_bf16(__uint_as_float(ra[v4 * 8 + 6]) * f, __uint_as_float(ra[v4 * 8 + 7]) * f);
+                *reinterpret_cast<uint4*>(orow + c * 16 + v4 * 8) = w;
               }
             }
           }
         }
       }
-    } else if (warp >= 8) {
-      // ------------------------------------------------------------ dQ drain: TMEM -> fp32 atomics
+    } else if (warp >= 12) {
+      // ------------------------------------------------------------ dQ drain: TMEM -> smem -> TMA reduce-add
+      // 32 columns at a time through two staging buffers.  Hand-offs use mbarriers with bounded
+      // waits (no named barriers: a role that gives up must never leave another one blocked).
       const int lane_base = (warp & 3) * 32;
+      const int row = lane_base + lane;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + T::COL_DQ;
+      const bool issuer = (threadIdx.x == 12 * 32);
+      const int swz = row & 7;
       bool ok = true;
       uint32_t r[32];
-      for (int n = 0; n < n_iter; ++n) {
-        const int q_row = (i0 + n) * T::BN + lane_base + lane;
+      int g = 0;   // chunks handled so far
+      for (int n = 0; n < n_iter && ok; ++n) {
         ok = mbar_wait(dq_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        float* dst = prm.dq_accum + (static_cast<size_t>(bh) * S + q_row) * D;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 32; ++c, ++g) {
+          const int buf = g & 1;
+          const uint32_t use = static_cast<uint32_t>(g >> 1);
+          uint8_t* stage = smem + T::SMEM_DQS + buf * T::BLOCK_BYTES;
           tmem_ld_x32(t_lane + c * 32, r);
           tmem_wait_ld();
-          if (c == D / 32 - 1) {   // last read done: the columns may be overwritten
+          if (c == D / 32 - 1) {   // the whole tile has left TMEM: dP^T of the next query tile may overwrite it
             tc_fence_before();
             mbar_arrive(dq_empty);
           }
-          if (q_row < S) {
+          // the reduce that read this buffer two chunks ago must be done with it
+          ok = mbar_wait(&dqs_free[buf], (use & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          uint8_t* dst = stage + row * 128;
 #pragma unroll
-            for (int v4 = 0; v4 < 8; ++v4)
-              atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + v4 * 4),
-                        make_float4(__uint_as_float(r[v4 * 4 + 0]), __uint_as_float(r[v4 * 4 + 1]),
-                                    __uint_as_float(r[v4 * 4 + 2]), __uint_as_float(r[v4 * 4 + 3])));
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(dst + ((ch ^ swz) << 4)) =
+                make_uint4(r[ch * 4 + 0], r[ch * 4 + 1], r[ch * 4 + 2], r[ch * 4 + 3]);
+          fence_proxy_async_smem();
+          mbar_arrive(&dqs_full[buf]);
+          if (issuer) {
+            if (mbar_wait(&dqs_full[buf], use & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX)) {
+              tma_reduce_add_3d(&tmap_dq, stage, c * 32, (i0 + n) * T::BN, bh);
+              bulk_commit_group();
+              if (g >= 1) {   // the previous chunk's reduce has read the other buffer: hand it back
+                bulk_wait_group_read<1>();
+                mbar_arrive(&dqs_free[buf ^ 1]);
+              }
+            }
           }
         }
       }
+      if (issuer) bulk_wait_group_all();   // shared memory must outlive the reads; results complete before exit
     }
   }
 

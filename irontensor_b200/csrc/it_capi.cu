@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <cmath>
@@ -198,6 +199,18 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causa
   if ((st = make_tmap(ctx, &mk, k, BH, S, D, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mv, v, BH, S, D, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mdo, d_o, BH, S, D, 128)) != IT_OK) return st;
+  // fp32 dQ accumulator [BH, S, D]: boxes of 32 columns x 128 rows for the TMA reduce-add
+  CUtensorMap mdq;
+  {
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(BH)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 4, static_cast<cuuint64_t>(S) * D * 4};
+    const cuuint32_t box[3] = {32, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = ctx->encode(&mdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ws + w.dq_accum_off, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(IT_ERR_CUDA, "cuTensorMapEncodeTiled (dQ accumulator) failed with %d", static_cast<int>(r));
+  }
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(it::fa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
@@ -226,7 +239,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causa
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const int n_kt = (S + 127) / 128;
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
-  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p);
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
