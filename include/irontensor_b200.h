@@ -163,6 +163,11 @@ it_status it_ctx_kernel_ms(it_ctx* ctx, int32_t which, float* ms);
  * In every variant out = a * (b as K x N). */
 it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, const void* a_bf16,
                            const void* b_bf16, float* out);
+/* Tensor-pipe issue-rate probe: `ctas` CTAs each issue iters*8 MMAs (128 x N x 16, operands resident
+ * on chip) through one operand path (0: A,B K-major smem N=128; 1: same N=256; 2: A in tensor memory,
+ * B N-major, N=128; 3: A M-major, B N-major, N=128; 4: as 2 with N=256).  The caller times the launch;
+ * FLOPs = ctas * iters * 8 * 2*128*N*16. */
+it_status it_selftest_umma_rate(it_ctx* ctx, it_stream* stream, int32_t variant, int32_t ctas, int32_t iters);
 /* Launches one CTA that waits `limit_ms` on a barrier nothing arrives on, so that the bounded-wait
  * path can be checked: afterwards it_attention_status_poll reports a non-zero word. */
 it_status it_selftest_wait_timeout(it_ctx* ctx, it_stream* stream, int32_t limit_ms);

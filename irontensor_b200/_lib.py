@@ -51,6 +51,7 @@ SIGNATURES = {
     "it_ctx_enable_kernel_timing": [_vp, _i32],
     "it_ctx_kernel_ms": [_vp, _i32, _c.POINTER(_c.c_float)],
     "it_selftest_umma": [_vp, _vp, _i32, _vp, _vp, _vp],
+    "it_selftest_umma_rate": [_vp, _vp, _i32, _i32, _i32],
     "it_selftest_wait_timeout": [_vp, _vp, _i32],
 }
 

@@ -209,8 +209,15 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   const bool bad_start = (*abort_flag != 0);
 
-  if (!bad_start && n_iter > 0) {
-    if (warp == 0) {
+  // Register budget: the control warpgroup (warps 0-3) keeps 96 per thread; what it gives up lets
+  // the dQ drain warpgroup (warps 12-15) hold a whole 128 x D fp32 tile in registers, so that tile
+  // leaves TMEM in one go.  128*96 + 256*128 + 128*160 = 65536 <= 65536.
+  const bool run = !bad_start && n_iter > 0;
+  if (warp < 4) {
+    setmaxnreg_dec<96>();
+    if (!run) {
+      // nothing to do
+    } else if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
       if (lane == 0) {
         prefetch_tensormap(&tmap_q);
@@ -342,7 +349,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         if (ok) umma_commit(dkv_done);
       }
-    } else if (warp >= 4 && warp < 12) {
+    }
+  } else if (warp < 12) {
+    if (run) {
       // ------------------------------------------------------------ P^T and dS^T math, dK/dV epilogue
       const int half = (warp - 4) >> 2;                 // which 64 of the 128 query columns
       const int lane_base = (warp & 3) * 32;
@@ -474,34 +483,37 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
         }
       }
-    } else if (warp >= 12) {
-      // ------------------------------------------------------------ dQ drain: TMEM -> smem -> TMA reduce-add
-      // 32 columns at a time through two staging buffers.  Hand-offs use mbarriers with bounded
-      // waits (no named barriers: a role that gives up must never leave another one blocked).
+    }
+  } else {
+    setmaxnreg_inc<160>();
+    if (run) {
+      // ------------------------------------------------------------ dQ drain: TMEM -> registers -> smem -> TMA reduce-add
+      // The tile is read out of TMEM in one go (so dP^T of the next query tile can start at once),
+      // then goes 32 columns at a time through two staging buffers.  Hand-offs use mbarriers with
+      // bounded waits (no named barriers: a role that gives up must never leave another one blocked).
       const int lane_base = (warp & 3) * 32;
       const int row = lane_base + lane;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + T::COL_DQ;
       const bool issuer = (threadIdx.x == 12 * 32);
       const int swz = row & 7;
       bool ok = true;
-      uint32_t r[32];
+      uint32_t r[D / 32][32];
       int g = 0;   // chunks handled so far
       for (int n = 0; n < n_iter && ok; ++n) {
         ok = mbar_wait(dq_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll 1
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld_x32(t_lane + c * 32, r[c]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(dq_empty);
+#pragma unroll
         for (int c = 0; c < D / 32; ++c, ++g) {
           const int buf = g & 1;
           const uint32_t use = static_cast<uint32_t>(g >> 1);
           uint8_t* stage = smem + T::SMEM_DQS + buf * T::BLOCK_BYTES;
-          tmem_ld_x32(t_lane + c * 32, r);
-          tmem_wait_ld();
-          if (c == D / 32 - 1) {   // the whole tile has left TMEM: dP^T of the next query tile may overwrite it
-            tc_fence_before();
-            mbar_arrive(dq_empty);
-          }
           // the reduce that read this buffer two chunks ago must be done with it
           ok = mbar_wait(&dqs_free[buf], (use & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY);
           ok = __all_sync(0xffffffffu, ok);
@@ -510,7 +522,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch)
             *reinterpret_cast<uint4*>(dst + ((ch ^ swz) << 4)) =
-                make_uint4(r[ch * 4 + 0], r[ch * 4 + 1], r[ch * 4 + 2], r[ch * 4 + 3]);
+                make_uint4(r[c][ch * 4 + 0], r[c][ch * 4 + 1], r[c][ch * 4 + 2], r[c][ch * 4 + 3]);
           fence_proxy_async_smem();
           mbar_arrive(&dqs_full[buf]);
           if (issuer) {

@@ -621,6 +621,30 @@ it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, cons
   return IT_OK;
 }
 
+it_status it_selftest_umma_rate(it_ctx* ctx, it_stream* stream, int32_t variant, int32_t ctas, int32_t iters) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  if (variant < 0 || variant > 4 || ctas < 1 || ctas > 1024 || iters < 1 || iters > 100000)
+    return fail(IT_ERR_INVALID_ARG, "variant 0..4, ctas 1..1024, iters 1..100000");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  const int smem = 6 * 128 * 128 + 64;
+#define IT_RATE_CASE(V)                                                                                      \
+  case V:                                                                                                    \
+    IT_CUDA(cudaFuncSetAttribute(it::umma_rate_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    it::umma_rate_kernel<V><<<ctas, 128, smem, stream->s>>>(iters, ctx->d_status);                           \
+    break;
+  switch (variant) {
+    IT_RATE_CASE(0)
+    IT_RATE_CASE(1)
+    IT_RATE_CASE(2)
+    IT_RATE_CASE(3)
+    IT_RATE_CASE(4)
+  }
+#undef IT_RATE_CASE
+  ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
 it_status it_selftest_wait_timeout(it_ctx* ctx, it_stream* stream, int32_t limit_ms) {
   if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
   if (limit_ms < 1 || limit_ms > 1000) return fail(IT_ERR_INVALID_ARG, "limit_ms must be in 1..1000");

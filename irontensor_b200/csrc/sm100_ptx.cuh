@@ -234,6 +234,13 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Per-warp register budget.  Executed by all four warps of an aligned warpgroup; `inc` waits until
+// the registers other warpgroups gave up with `dec` are available.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---------------------------------------------------------------- small math / packing helpers
 __device__ __forceinline__ float ex2(float x) {
   float y;
