@@ -77,9 +77,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int S = prm.S;
   const int n_kv_total = (S + T::BN - 1) / T::BN;
   const int n_pairs = (S + 2 * T::BM - 1) / (2 * T::BM);
-  // Heaviest (last) query tiles of every head first.
-  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) / prm.BH;
-  const int bh = static_cast<int>(blockIdx.x) % prm.BH;
+  // Head-major order: the CTAs resident at one time belong to a few (batch, head) slices, so the K/V
+  // tiles they all stream stay in L2.  Within a slice the last query tiles (most keys) go first.
+  const int bh = static_cast<int>(blockIdx.x) / n_pairs;
+  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) % n_pairs;
   int n_kv[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -122,8 +123,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   const bool bad_start = (*abort_flag != 0);
 
-  if (!bad_start) {
-    if (warp == 0) {
+  // Register budget: the control warpgroup keeps 80 per thread, the two softmax warpgroups take
+  // 208 each so that a whole 128-column row of S stays in registers (128*80 + 256*208 = 63488).
+  if (warp < 4) {
+    setmaxnreg_dec<80>();
+    if (bad_start) {
+      // nothing to do
+    } else if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
       if (lane == 0) {
         prefetch_tensormap(&tmap_q);
@@ -211,113 +217,118 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (have_next) umma_commit(&k_empty[st_n]);
         }
       }
-    } else if (warp >= 4) {
-      // ------------------------------------------------------------ softmax + epilogue
-      const int t = (warp - 4) >> 2;
-      const int nkv = n_kv[t];
-      if (nkv > 0) {
-        const int qt = 2 * pair + t;
-        const int lane_base = (warp & 3) * 32;
-        const int q_row = qt * T::BM + lane_base + lane;
-        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + t * 128;
-        const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + 256 + t * D;
-        const float sl2 = prm.scale_log2;
-        float m_used = -INFINITY;
-        float l_sum = 0.f;
-        bool ok = true;
-        uint32_t r[32];
-        for (int j = 0; j < nkv; ++j) {
-          ok = mbar_wait(&s_full[t], j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          const bool need_mask = (prm.causal && j == qt) || ((j + 1) * T::BN > S);
-          const int kbase = j * T::BN;
-          const int k_limit = prm.causal ? min(S - 1, q_row) : (S - 1);   // last visible key index
-          // pass 1: row maximum
-          float mx = -INFINITY;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld_x32(t_s + c * 32, r);
-            tmem_wait_ld();
-            if (need_mask) {
+    }
+  } else {
+    setmaxnreg_inc<208>();
+    // ------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 4) >> 2;
+    const int nkv = n_kv[t];
+    if (!bad_start && nkv > 0) {
+      const int qt = 2 * pair + t;
+      const int lane_base = (warp & 3) * 32;
+      const int q_row = qt * T::BM + lane_base + lane;
+      const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + t * 128;
+      const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + 256 + t * D;
+      const float sl2 = prm.scale_log2;
+      const int k_limit = prm.causal ? min(S - 1, q_row) : (S - 1);   // last visible key index
+      float m_used = -INFINITY;
+      float l_sum = 0.f;
+      bool ok = true;
+      uint32_t r[128];   // this thread's row of S
+      for (int j = 0; j < nkv; ++j) {
+        ok = mbar_wait(&s_full[t], j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        // the whole row in one go: four loads in flight, one wait
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (kbase + c * 32 + i <= k_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
-            } else {
+        for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tmem_wait_ld();
+        if ((prm.causal && j == qt) || ((j + 1) * T::BN > S)) {   // diagonal or ragged last tile
+          const int vis = k_limit - j * T::BN;   // columns 0..vis are visible
 #pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-            }
-          }
-          const float m_new = mx * sl2;
-          if (j == 0) {
-            m_used = m_new;
-          } else {
-            const bool grow = m_new > m_used + 8.0f;
-            if (__any_sync(0xffffffffu, grow)) {
-              const float m_next = fmaxf(m_used, m_new);
-              const float f = ex2(m_used - m_next);
-              l_sum *= f;
-              m_used = m_next;
-#pragma unroll 1
-              for (int c = 0; c < D / 32; ++c) {
-                tmem_ld_x32(t_o + c * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-                tmem_st_x32(t_o + c * 32, r);
-              }
-              tmem_wait_st();
-            }
-          }
-          // pass 2: P = 2^(s*scale - m), packed bf16 written over S
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld_x32(t_s + c * 32, r);
-            tmem_wait_ld();
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float p0 = ex2(fmaf(__uint_as_float(r[i]), sl2, -m_used));
-              float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sl2, -m_used));
-              if (need_mask) {
-                if (kbase + c * 32 + i > k_limit) p0 = 0.f;
-                if (kbase + c * 32 + i + 1 > k_limit) p1 = 0.f;
-              }
-              l_sum += p0 + p1;
-              pk[i >> 1] = pack_bf16(p0, p1);
-            }
-            tmem_st_x16(t_s + c * 16, pk);
-          }
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&p_full[t]);
+          for (int i = 0; i < 128; ++i)
+            if (i > vis) r[i] = 0xFF800000u;     // -inf: drops out of the max, exp2 gives 0
         }
-        if (ok) {
-          ok = mbar_wait(&o_done[t], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
-          ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-          tc_fence_after();
-          const float inv_l = 1.0f / l_sum;
-          __nv_bfloat16* orow = prm.o + (static_cast<size_t>(bh) * S + q_row) * D;
-#pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            tmem_ld_x32(t_o + c * 32, r);
-            tmem_wait_ld();
-            if (q_row < S) {
+        float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]), mx2 = __uint_as_float(r[2]),
+              mx3 = __uint_as_float(r[3]);
 #pragma unroll
-              for (int v4 = 0; v4 < 4; ++v4) {
-                uint4 w;
-                w.x = pack_bf16(__uint_as_float(r[v4 * 8 + 0]) * inv_l, __uint_as_float(r[v4 * 8 + 1]) * inv_l);
-                w.y = pack_bf16(__uint_as_float(r[v4 * 8 + 2]) * inv_l, __uint_as_float(r[v4 * 8 + 3]) * inv_l);
-                w.z = pack_bf16(__uint_as_float(r[v4 * 8 + 4]) * inv_l, __uint_as_float(r[v4 * 8 + 5]) * inv_l);
-                w.w = pack_bf16(__uint_as_float(r[v4 * 8 + 6]) * inv_l, __uint_as_float(r[v4 * 8 + 7]) * inv_l);
-                *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = w;
-              }
+        for (int i = 4; i < 128; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+        }
+        const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+        if (j == 0) {
+          m_used = m_new;
+        } else {
+          const bool grow = m_new > m_used + 8.0f;
+          if (__any_sync(0xffffffffu, grow)) {   // rare: raise the reference and rescale O in TMEM
+            const float m_next = fmaxf(m_used, m_new);
+            const float f = ex2(m_used - m_next);
+            l_sum *= f;
+            m_used = m_next;
+            uint32_t tmp[16];
+#pragma unroll 1
+            for (int c = 0; c < D / 16; ++c) {
+              tmem_ld_x16(t_o + c * 16, tmp);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) tmp[i] = __float_as_uint(__uint_as_float(tmp[i]) * f);
+              tmem_st_x16(t_o + c * 16, tmp);
             }
+            tmem_wait_st();
           }
-          if (prm.lse != nullptr && q_row < S)
+        }
+        // P = 2^(s*scale - m), packed bf16, written over S 32 keys at a time
+        const float neg_m = -m_used;
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = ex2(fmaf(__uint_as_float(r[c * 32 + i + 0]), sl2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(r[c * 32 + i + 1]), sl2, neg_m));
+            const float p2 = ex2(fmaf(__uint_as_float(r[c * 32 + i + 2]), sl2, neg_m));
+            const float p3 = ex2(fmaf(__uint_as_float(r[c * 32 + i + 3]), sl2, neg_m));
+            l0 += p0;
+            l1 += p1;
+            l2 += p2;
+            l3 += p3;
+            pk[(i >> 1)] = pack_bf16(p0, p1);
+            pk[(i >> 1) + 1] = pack_bf16(p2, p3);
+          }
+          tmem_st_x16(t_s + c * 16, pk);
+        }
+        l_sum += (l0 + l1) + (l2 + l3);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[t]);
+      }
+      if (ok) {
+        ok = mbar_wait(&o_done[t], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = 1.0f / l_sum;
+        __nv_bfloat16* orow = prm.o + (static_cast<size_t>(bh) * S + q_row) * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld_x32(t_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tmem_wait_ld();
+        if (q_row < S) {
+#pragma unroll
+          for (int v = 0; v < D / 8; ++v) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
+            w.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
+            w.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
+            w.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + v * 8) = w;
+          }
+          if (prm.lse != nullptr)
             prm.lse[static_cast<size_t>(bh) * S + q_row] = (m_used + lg2(l_sum)) * 0.6931471805599453f;
         }
       }
