@@ -13,8 +13,9 @@ is used only for the barrier and the max-over-ranks of the device times.
 Prints ONE JSON line:
   value        whole-job TFLOP/s with inputs resident in HBM (FLOPs: fwd 2*B*H*S^2*D, bwd 5*B*H*S^2*D,
                the causal-halved FlashAttention convention), device time from CUDA events, max over ranks
-  e2e          the same metric through the package's public ops with HOST tensors: every step uploads
-               Q,K,V,dO from pinned memory and downloads O,dQ,dK,dV inside the timed region
+  e2e          the same metric through the package's public ops with HOST tensors (HostAttentionStep):
+               every step uploads Q,K,V,dO from pinned memory and downloads O,dQ,dK,dV inside the timed
+               region, slices in 8 groups on rotating streams so copies and kernels overlap
   roofline     the backward main kernel (dominant) against the measured dense-bf16 peak
   cpu_baseline the CPU oracle timed on this box's host cores on a bounded sample (rank 0, N=1 only)
 --impl reference times the reference's algorithm on the host cores instead (the CPU oracle: the
@@ -255,14 +256,11 @@ def run_ours(args, rank, world, local_rank):
         return
     hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, d_o))
     ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
-    shape = [1, n, S, D]
-    tq, tk, tv, tdo = (Tensor.empty(shape, Precision.BF16) for _ in range(4))
+    from irontensor_b200 import HostAttentionStep
+    pipe = HostAttentionStep(n, S, D, Precision.BF16, causal=True, chunks=8)
 
     def step_e2e():
-        tq.upload_from(hq), tk.upload_from(hk), tv.upload_from(hv), tdo.upload_from(hdo)
-        out = flash_attention(tq, tk, tv, True)
-        gq, gk, gv = attention_backward_recompute(tdo, tq, tk, tv, o=out, lse=out.lse)
-        out.download_to(ho), gq.download_to(hdq), gk.download_to(hdk), gv.download_to(hdv)
+        pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv)
 
     e2e_steps = steps
     if nbh:
@@ -320,13 +318,98 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_small(args):
+    """Secondary, single-GPU reports for the small configurations (not the headline line):
+    c1 = fp32 forward B16 H4 S256 D64; c5 = the greedy no-KV-cache pattern, fp32 forward at every prefix
+    length 20..119 (100 calls), eager and replayed from one CUDA graph.  Device-resident inputs, CUDA events."""
+    import torch
+    from irontensor_b200 import _lib, context, raw
+    torch.cuda.set_device(0)
+    ctx = context(0)
+    peaks = measured_peaks()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x1A7E5EED + (1 if args.workload == "c1" else 5))
+
+    def timed(fn, reps, flush_l2):
+        ts = []
+        for i in range(reps):
+            if flush_l2:
+                flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts), min(ts)
+
+    if args.workload == "c1":
+        B, H, S, D = 16, 4, 256, 64
+        q, k, v = (torch.randn((B, H, S, D), generator=gen, device="cuda") for _ in range(3))
+        o = torch.empty_like(q)
+        lse = torch.empty((B, H, S), device="cuda")
+
+        def f():
+            raw.fwd(_lib.IT_F32, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
+        for _ in range(max(args.warmup, 3)):
+            f()
+        med_cold, min_cold = timed(f, args.steps, True)
+        med_warm, min_warm = timed(f, args.steps, False)
+        flops, nbytes = 2.0 * B * H * S * S * D, 4 * B * H * S * D * 4 + B * H * S * 4
+        line = {"metric": "causal attention forward latency", "unit": "us", "value": med_cold, "higher_is_better": False,
+                "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "causal fp32 attention forward B16 H4 S256 D64", "l2": "flushed between calls (value); warm figures alongside"},
+                "us_min": min_cold, "us_warm_l2": med_warm, "gbs": nbytes / med_cold / 1e3, "gbs_warm_l2": nbytes / med_warm / 1e3,
+                "tflops": flops / med_cold / 1e6, "roofline": {"bound": "hbm", "achieved": nbytes / med_cold / 1e3, "peak": peaks["hbm"],
+                                                               "unit": "GB/s", "frac": nbytes / med_cold / 1e3 / peaks["hbm"], "traffic": None}}
+        print(json.dumps(line), flush=True)
+        return
+    # c5
+    H, D = 4, 64
+    lens = list(range(20, 120))
+    bufs = []
+    for S in lens:
+        q, k, v = (torch.randn((1, H, S, D), generator=gen, device="cuda") for _ in range(3))
+        bufs.append((S, q, k, v, torch.empty_like(q), torch.empty((1, H, S), device="cuda")))
+
+    def seq():
+        for S, q, k, v, o, lse in bufs:
+            raw.fwd(_lib.IT_F32, 1, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
+    for _ in range(max(args.warmup, 3)):
+        seq()
+    torch.cuda.synchronize()
+    med_eager, min_eager = timed(seq, args.steps, False)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        seq()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            seq()
+    torch.cuda.synchronize()
+    med_graph, min_graph = timed(graph.replay, args.steps, False)
+    flops = sum(512.0 * S * S for S in lens)
+    nbytes = sum(4112.0 * S for S in lens)
+    line = {"metric": "greedy no-KV-cache attention forward, per-call latency", "unit": "us", "value": med_graph / len(lens),
+            "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "f32",
+            "data": "synthetic", "config": {"workload": "fp32 causal forward B1 H4 D64 at prefix lengths 20..119 (100 calls)",
+                                            "note": "value = one CUDA-graph replay of the 100 calls / 100; tensors stay in L2 (28.6 MB in total)"},
+            "us_per_call_eager": med_eager / len(lens), "us_per_call_graph_min": min_graph / len(lens),
+            "gbs": nbytes / med_graph / 1e3, "tflops": flops / med_graph / 1e6,
+            "roofline": {"bound": "hbm", "achieved": nbytes / med_graph / 1e3, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": nbytes / med_graph / 1e3 / peaks["hbm"], "traffic": None,
+                         "note": "launch-latency bound: the HBM time of the longest call is 0.08 us"}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
     ap.add_argument("--slices", type=int, default=0,
@@ -343,6 +426,10 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", port, os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
+    if args.workload in ("c1", "c5"):
+        if rank == 0:
+            run_small(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

@@ -1,8 +1,9 @@
 // CUDA-core attention kernels with fp32 arithmetic: the path for fp32 tensors (the reference's
 // FP32 mode, src/ops/flash_attention.rs:76-193) and for bf16 shapes the tensor-core kernels do not
 // take (head_dim other than 64/128, sequences shorter than one 128-row tile).  Any S >= 1, any
-// 1 <= D <= 128, causal or full.  Storage type ST is float or __nv_bfloat16; math is fp32 with
-// libm-accurate expf/logf so the fp32 mode stays within 1e-4 of the reference's scalar kernels.
+// 1 <= D <= 128, causal or full.  Storage type ST is float or __nv_bfloat16; math is fp32, the
+// exponentials in the exp2 domain (ex2.approx / lg2.approx, relative error 2^-22), which keeps the
+// fp32 mode within 1e-4 (measured: 2e-6) of the reference's scalar kernels.
 //
 // Forward: a CTA owns 64 query rows of one (batch, head); four threads share a row, each holding
 // a quarter of the head dimension of q and of the output accumulator.  Keys and values stream
@@ -15,6 +16,17 @@
 #include <cstdint>
 
 namespace it {
+
+__device__ __forceinline__ float g_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float g_lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <typename ST> __device__ __forceinline__ float ld_as_f32(const ST* p);
 template <> __device__ __forceinline__ float ld_as_f32<float>(const float* p) { return *p; }
@@ -31,7 +43,7 @@ template <> __device__ __forceinline__ void st_from_f32<__nv_bfloat16>(__nv_bflo
 template <typename ST, int DP>
 __global__ void __launch_bounds__(256)
 fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
-                      ST* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale) {
+                      ST* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2) {
   constexpr int BM = 64;
   constexpr int BN = (DP >= 128) ? 32 : 64;
   constexpr int NCH = DP / 16;              // float4 chunks per thread
@@ -92,7 +104,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
         a += __shfl_xor_sync(0xffffffffu, a, 2);
         const int kidx = k0 + g0 + kk;
         const bool vis = (g0 + kk < nk) && (!causal || kidx <= row);
-        sc[kk] = vis ? a * scale : -INFINITY;
+        sc[kk] = vis ? a * scale_log2 : -INFINITY;
       }
       float gmax = sc[0];
 #pragma unroll
@@ -100,7 +112,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
       const float m_new = fmaxf(m_run, gmax);
       // Nothing visible to this row yet: keep the state at (-inf, 0) without producing NaN.
       const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = expf(m_run - m_ref);
+      const float corr = g_ex2(m_run - m_ref);
       l_run *= corr;
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
@@ -108,7 +120,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
       }
 #pragma unroll
       for (int kk = 0; kk < 16; ++kk) {
-        const float p = expf(sc[kk] - m_ref);
+        const float p = g_ex2(sc[kk] - m_ref);
         l_run += p;
         const float4* vr = reinterpret_cast<const float4*>(sV + (g0 + kk) * DP);
 #pragma unroll
@@ -133,7 +145,165 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
       for (int e = 0; e < 4; ++e)
         if (d0 + e < D) st_from_f32(o + base + static_cast<size_t>(row) * D + d0 + e, tmp[e]);
     }
-    if (lse != nullptr && t4 == 0) lse[static_cast<size_t>(bh) * S + row] = m_run + logf(l_run);
+    if (lse != nullptr && t4 == 0)
+      lse[static_cast<size_t>(bh) * S + row] = (m_run + g_lg2(l_run)) * 0.6931471805599453f;
+  }
+}
+
+// fp32 tensors with D a multiple of 4 and short to medium sequences: the latency path (the greedy
+// no-KV-cache inference pattern re-runs it once per generated token, and the reference's TINY model
+// sits at S = 256).  A CTA owns 16 consecutive query rows of one head, four per warp.  Keys and
+// values stream through shared memory 32 at a time (cp.async, double buffered, rows padded by four
+// floats so that lane-per-key float4 reads are conflict free).  Scores: one key per lane, each K
+// chunk read once and used for the warp's four rows; softmax: online, warp-reduced per tile (the
+// recurrence of src/shaders/flash_attention.metal:27-41); output: lanes over the head dimension,
+// the tile's probabilities parked in shared memory and read back four keys at a time, V read from
+// shared memory.  NJ = ceil(D / 32) output elements per lane.
+template <int NJ>
+__global__ void __launch_bounds__(128)
+fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                       float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2) {
+  constexpr int RB = 16, RW = 4, TK = 32;
+  extern __shared__ __align__(16) float sm[];
+  const int DS = D + 4;                       // padded row stride (floats)
+  float* sQ = sm;                             // [RB][D]
+  float* sK = sQ + RB * D;                    // [2][TK][DS]
+  float* sV = sK + 2 * TK * DS;               // [2][TK][DS]
+  float* sP = sV + 2 * TK * DS;               // [4 warps][RW][TK] probabilities of the current tile
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nd4 = D >> 2;
+  const int n_rb = (S + RB - 1) / RB;
+  const int rb = n_rb - 1 - static_cast<int>(blockIdx.x);    // longest rows first
+  const int bh = blockIdx.y;
+  const int r0 = rb * RB;
+  const size_t base = static_cast<size_t>(bh) * S * D;
+  const int k_end_cta = causal ? min(S, r0 + RB) : S;
+  const int n_tiles = (k_end_cta + TK - 1) / TK;
+
+  auto load_tile = [&](int tile, int buf) {
+    const int k0 = tile * TK;
+    float* dk = sK + buf * TK * DS;
+    float* dv = sV + buf * TK * DS;
+    for (int idx = tid; idx < TK * nd4; idx += 128) {
+      const int key = idx / nd4, c = idx - key * nd4;
+      float* pk = dk + key * DS + 4 * c;
+      float* pv = dv + key * DS + 4 * c;
+      if (k0 + key < k_end_cta) {
+        const size_t g = base + static_cast<size_t>(k0 + key) * D + 4 * c;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(pk))), "l"(k + g));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(pv))), "l"(v + g));
+      } else {   // rows past the end: zeros, so that 0 * V stays 0
+        *reinterpret_cast<float4*>(pk) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(pv) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  load_tile(0, 0);
+  for (int idx = tid; idx < RB * nd4; idx += 128) {
+    const int rr = idx / nd4, c = idx - rr * nd4;
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r0 + rr < S) val = reinterpret_cast<const float4*>(q + base + static_cast<size_t>(r0 + rr) * D)[c];
+    reinterpret_cast<float4*>(sQ + rr * D)[c] = val;
+  }
+
+  float m_run[RW], l_run[RW], acc[RW][NJ];
+  int lim[RW];                                  // last visible key of each of this warp's rows
+#pragma unroll
+  for (int w = 0; w < RW; ++w) {
+    const int row = r0 + warp * RW + w;
+    m_run[w] = -INFINITY;
+    l_run[w] = 0.f;
+    lim[w] = (row < S) ? (causal ? row : S - 1) : -1;
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) acc[w][jj] = 0.f;
+  }
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int buf = tile & 1;
+    if (tile + 1 < n_tiles) {
+      load_tile(tile + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int k0 = tile * TK;
+    if (k0 <= max(max(lim[0], lim[1]), max(lim[2], lim[3]))) {   // some row of this warp sees a key of the tile
+      const float4* kp = reinterpret_cast<const float4*>(sK + buf * TK * DS + lane * DS);
+      const float4* qp = reinterpret_cast<const float4*>(sQ + warp * RW * D);
+      float dot[RW] = {0.f, 0.f, 0.f, 0.f}, dot2[RW] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int c = 0; c < nd4; ++c) {
+        const float4 kv = kp[c];
+#pragma unroll
+        for (int w = 0; w < RW; ++w) {
+          const float4 qv = qp[w * nd4 + c];
+          dot[w] = fmaf(qv.x, kv.x, dot[w]);
+          dot2[w] = fmaf(qv.y, kv.y, dot2[w]);
+          dot[w] = fmaf(qv.z, kv.z, dot[w]);
+          dot2[w] = fmaf(qv.w, kv.w, dot2[w]);
+        }
+      }
+      float* pw = sP + warp * RW * TK;
+      float p[RW];
+#pragma unroll
+      for (int w = 0; w < RW; ++w) {
+        const float s2 = (k0 + lane <= lim[w]) ? (dot[w] + dot2[w]) * scale_log2 : -INFINITY;
+        float tmax = s2;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+        const float m_new = fmaxf(m_run[w], tmax);
+        const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;   // nothing visible yet: stay at (-inf, 0)
+        p[w] = g_ex2(s2 - m_ref);
+        pw[w * TK + lane] = p[w];
+        float psum = p[w];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, off);
+        const float corr = g_ex2(m_run[w] - m_ref);
+        l_run[w] = l_run[w] * corr + psum;
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) acc[w][jj] *= corr;
+        m_run[w] = m_new;
+      }
+      __syncwarp();
+      const float* vp = sV + buf * TK * DS + lane;
+#pragma unroll 2
+      for (int kk = 0; kk < TK; kk += 4) {
+        float4 p4[RW];
+#pragma unroll
+        for (int w = 0; w < RW; ++w) p4[w] = *reinterpret_cast<const float4*>(pw + w * TK + kk);   // broadcast read
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float vv[NJ];
+#pragma unroll
+          for (int jj = 0; jj < NJ; ++jj) vv[jj] = (lane + 32 * jj < D) ? vp[(kk + e) * DS + 32 * jj] : 0.f;
+#pragma unroll
+          for (int w = 0; w < RW; ++w) {
+            const float pk = e == 0 ? p4[w].x : e == 1 ? p4[w].y : e == 2 ? p4[w].z : p4[w].w;
+#pragma unroll
+            for (int jj = 0; jj < NJ; ++jj) acc[w][jj] = fmaf(pk, vv[jj], acc[w][jj]);
+          }
+        }
+      }
+      __syncwarp();   // the warp's probability buffer is rewritten by the next tile
+    }
+    __syncthreads();   // everyone is done with this buffer before the next load overwrites it
+  }
+#pragma unroll
+  for (int w = 0; w < RW; ++w) {
+    const int row = r0 + warp * RW + w;
+    if (row < S) {
+      const float inv = 1.0f / l_run[w];
+#pragma unroll
+      for (int jj = 0; jj < NJ; ++jj) {
+        const int d = lane + 32 * jj;
+        if (d < D) o[base + static_cast<size_t>(row) * D + d] = acc[w][jj] * inv;
+      }
+      if (lse != nullptr && lane == 0)
+        lse[static_cast<size_t>(bh) * S + row] = (m_run[w] + g_lg2(l_run[w])) * 0.6931471805599453f;
+    }
   }
 }
 
@@ -214,7 +384,7 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
     }
     const float lse_x = (MODE == 0) ? lse_r : lse_h[x];
     const float dl_x = (MODE == 0) ? dl_r : dl_h[x];
-    const float p = expf(s * scale - lse_x);
+    const float p = g_ex2(fmaf(s, scale * 1.4426950408889634f, -lse_x * 1.4426950408889634f));
     const float ds = p * (dp - dl_x);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {

@@ -102,10 +102,32 @@ int round_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128; }
 template <typename ST>
 void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
                         const void* v, void* o, float* lse) {
-  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  const float scale = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;   // exp2 domain
   const dim3 grid((S + 63) / 64, BH);
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
   ST* oo = static_cast<ST*>(o);
+  if (sizeof(ST) == 4 && S <= 2048 && (D & 3) == 0) {   // fp32, short to medium sequences: the latency path
+    const int smem = (16 * D + 4 * 32 * (D + 4) + 4 * 4 * 32) * 4;
+    const dim3 g16((S + 15) / 16, BH);
+    const float *qf = reinterpret_cast<const float*>(q), *kf = reinterpret_cast<const float*>(k),
+                *vf = reinterpret_cast<const float*>(v);
+    float* of = reinterpret_cast<float*>(o);
+    if (D <= 32) {
+      it::fa_fwd_rows_f32_kernel<1><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale);
+    } else if (D <= 64) {
+      it::fa_fwd_rows_f32_kernel<2><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale);
+    } else {
+      static bool attr_set[16] = {};
+      if (!attr_set[ctx->device & 15]) {
+        cudaFuncSetAttribute(it::fa_fwd_rows_f32_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (16 * 128 + 4 * 32 * 132 + 512) * 4);
+        attr_set[ctx->device & 15] = true;
+      }
+      it::fa_fwd_rows_f32_kernel<4><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale);
+    }
+    ctx->launches += 1;
+    return;
+  }
   switch (round_dp(D)) {
     case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
     case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;

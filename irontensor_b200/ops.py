@@ -305,11 +305,12 @@ def _workspace(nbytes):
     """Grow-only scratch buffer per device (the ops allocate outputs like the reference does; the
     C ABI itself never allocates)."""
     torch = _torch()
-    dev = torch.cuda.current_device()
-    w = _workspaces.get(dev)
+    # one buffer per (device, stream): calls on different streams may run at the same time
+    key = (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+    w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
         w = torch.empty(max(nbytes, 256), dtype=torch.uint8, device="cuda")
-        _workspaces[dev] = w
+        _workspaces[key] = w
     return w
 
 
@@ -392,3 +393,47 @@ def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=
     raw.bwd(code, B, H, S, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(),
             lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
     return dq, dk, dv
+
+
+class HostAttentionStep:
+    """Forward + backward for tensors that live in page-locked HOST memory.
+
+    The reference's tensors are unified memory, so its ops never copy; on a discrete GPU a caller with
+    host data pays PCIe both ways.  This helper hides most of it: the (batch*head) slices are cut into
+    `chunks` groups, and each group runs upload -> flash_attention -> attention_backward_recompute ->
+    download on its own stream (three streams in rotation), so one group's upload, another's kernels
+    and a third's download proceed at the same time on the two copy engines and the SMs.
+    Device buffers are allocated once, in the constructor."""
+
+    def __init__(self, n_slices, S, D, precision=Precision.BF16, causal=True, chunks=4, n_streams=3):
+        torch = _torch()
+        self.S, self.D, self.precision, self.causal = S, D, precision, causal
+        chunks = max(1, min(chunks, n_slices))
+        per = -(-n_slices // chunks)
+        self.ranges = [(b, min(n_slices, b + per)) for b in range(0, n_slices, per)]
+        self.streams = [torch.cuda.Stream() for _ in range(min(n_streams, len(self.ranges)))]
+        self.dev = [[Tensor.empty([1, per, S, D], precision) for _ in range(4)] for _ in self.streams]
+        self.done = [torch.cuda.Event() for _ in self.streams]
+
+    def run(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv):
+        """All arguments: pinned torch tensors [n_slices, S, D].  Enqueues the whole step; the calling
+        stream continues only after every group's download has finished."""
+        torch = _torch()
+        cur = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(cur)
+        for i, (b0, b1) in enumerate(self.ranges):
+            st = self.streams[i % len(self.streams)]
+            bufs = self.dev[i % len(self.streams)]
+            n = b1 - b0
+            shape = [1, n, self.S, self.D]
+            with torch.cuda.stream(st):
+                st.wait_event(start)
+                tq, tk, tv, tdo = (Tensor(t._data[: n * self.S * self.D], shape, self.precision) for t in bufs)
+                tq.upload_from(hq[b0:b1]), tk.upload_from(hk[b0:b1]), tv.upload_from(hv[b0:b1]), tdo.upload_from(hdo[b0:b1])
+                out = flash_attention(tq, tk, tv, self.causal)
+                gq, gk, gv = attention_backward_recompute(tdo, tq, tk, tv, o=out, lse=out.lse, causal=self.causal)
+                out.download_to(ho[b0:b1]), gq.download_to(hdq[b0:b1]), gk.download_to(hdk[b0:b1]), gv.download_to(hdv[b0:b1])
+                self.done[i % len(self.streams)].record(st)
+        for ev in self.done:
+            cur.wait_event(ev)

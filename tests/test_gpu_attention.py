@@ -356,3 +356,23 @@ def test_ops_mirror_reference_interface(it_ctx):
     assert ob.precision() is Precision.BF16
     ref = ol.fwd(synth.round_bf16(g["q"]), synth.round_bf16(g["k"]), synth.round_bf16(g["v"]), True)[0]
     assert np.abs(ob.to_f32_host() - ref).max() <= BF16_MAX_ABS
+
+
+def test_host_step_overlapped_chunks_match_device_resident(it_ctx):
+    """HostAttentionStep (pinned host tensors, chunked over streams) gives the bytes of one device-resident run."""
+    import torch
+    from irontensor_b200 import HostAttentionStep, Precision
+    BH, S, D = 10, 256, 64     # 10 slices in 4 chunks: 3,3,3,1
+    q, k, v, d_o = seeded(77, 1, BH, S, D, bf16=True)
+    whole = gu.run_fwd_bwd(it_ctx, q, k, v, d_o, True, True)
+    host_in = [gu.to_dev(x[0], True).cpu().pin_memory() for x in (q, k, v, d_o)]
+    host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(4)]
+    step = HostAttentionStep(BH, S, D, Precision.BF16, causal=True, chunks=4)
+    for _ in range(2):   # twice: buffers and streams are reused
+        step.run(*host_in, *host_out)
+        torch.cuda.synchronize()
+    assert it_ctx.poll_status() == 0
+    got = [gu.to_host(t) for t in host_out]   # O, dQ, dK, dV
+    assert np.array_equal(got[0], whole[0][0])
+    assert np.abs(got[1] - whole[2][0]).max() <= 2e-2     # dQ: reduction order may differ
+    assert np.array_equal(got[2], whole[3][0]) and np.array_equal(got[3], whole[4][0])
