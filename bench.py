@@ -42,10 +42,9 @@ WORKLOADS = {
 METRIC = "causal attention fwd+bwd TFLOP/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of fa_bwd_sm100_kernel from an ncu capture:
-# profiles/fa_bwd_sm100_c4_32slices_ncu.md measured 1.968 GB + 1.013 GB on 32 of the 64 slices; traffic
+# profiles/fa_bwd_sm100_c4_32slices_ncu.md measured 0.405 GB + 0.225 GB on 32 of the 64 slices; traffic
 # grows in proportion to the slices a launch processes, so the full launch is twice that.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c4": 2 * (1.967934e9 + 1.012733e9)}
-
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c4": 2 * (405.263360e6 + 224.876544e6)}
 
 def flops_fwd(bh, S, D):
     return 2.0 * bh * S * S * D
@@ -121,6 +120,7 @@ def cpu_oracle_rate(S, D, qk_scale, n_slices, seed):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
     from irontensor_b200 import synth
+    ol.oracle().oracle_set_num_threads(os.cpu_count() or 1)   # torchrun sets OMP_NUM_THREADS=1
     q, k, v, d_o = [t.reshape(1, n_slices, S, D) for t in
                     synth.attention_inputs(seed, 1, n_slices, S, D, bf16=True, qk_scale=qk_scale)]
     ol.fwd(q[:, :1, :256], k[:, :1, :256], v[:, :1, :256])   # load the library, warm the thread pool

@@ -315,6 +315,15 @@ int oracle_attention_bwd(int B, int H, int S, int D, int causal,
   return 0;
 }
 
+// Launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU legs ask for all cores again.
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
