@@ -1,0 +1,283 @@
+// C++ host-side mirror of the reference's attention interface over the C ABI (irontensor_b200.h).
+//
+// The reference is a Rust crate; with no Rust toolchain to build against, this header is the
+// compiled-language host layer: same names, argument meaning and error behaviour as
+//   Precision, Tensor            src/precision.rs:1-29, src/tensor.rs:11-300
+//   CommandBatch                 src/command_batch.rs:167-391
+//   flash_attention              src/ops/flash_attention.rs:76-193     [B,H,S,D]
+//   attention                    src/ops/attention.rs:286-377          [B,S,H,D]
+//   attention_backward_recompute src/train/helpers.rs:120-193          [B,H,S,D]
+// Where the reference panics (assert!), these throw std::logic_error with the same message; failures of
+// the library itself throw it::Error carrying the status code.  Header-only; link libirontensor_b200.so.
+// No CPU fallback: every operation needs the CUDA library and a device.
+#pragma once
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "irontensor_b200.h"
+
+namespace it {
+
+struct Error : std::runtime_error {
+  it_status status;
+  Error(it_status s, const std::string& what) : std::runtime_error(what), status(s) {}
+};
+inline void check(it_status s) {
+  if (s != IT_OK) throw Error(s, it_last_error());
+}
+inline void require(bool cond, const char* msg) {
+  if (!cond) throw std::logic_error(msg);
+}
+
+enum class Precision { FP32, BF16 };
+inline size_t byte_size(Precision p) { return p == Precision::FP32 ? 4 : 2; }
+
+// src/precision.rs:24-29
+inline uint16_t f32_to_bf16(float x) {
+  uint32_t bits;
+  std::memcpy(&bits, &x, 4);
+  const uint32_t round = ((bits >> 16) & 1u) + 0x7FFFu;
+  return static_cast<uint16_t>((bits + round) >> 16);
+}
+inline float bf16_to_f32(uint16_t x) {
+  const uint32_t bits = static_cast<uint32_t>(x) << 16;
+  float f;
+  std::memcpy(&f, &bits, 4);
+  return f;
+}
+
+// The process-wide device context and the calling thread's stream (MetalContext::global,
+// src/device.rs:27-29; the thread-local CommandBatch, src/command_batch.rs:49-53).
+class Context {
+ public:
+  static Context& global(int device = 0) {
+    static Context ctx(device);
+    return ctx;
+  }
+  it_ctx* raw() const { return ctx_; }
+  it_stream* stream() {
+    thread_local it_stream* s = nullptr;
+    if (s == nullptr) check(it_stream_create(ctx_, &s));
+    return s;
+  }
+
+ private:
+  explicit Context(int device) { check(it_ctx_create(device, &ctx_)); }
+  ~Context() { it_ctx_destroy(ctx_); }
+  it_ctx* ctx_ = nullptr;
+};
+
+struct CommandBatch {
+  static void begin() { active() = true; }
+  static bool is_active() { return active(); }
+  static void sync() { check(it_stream_sync(Context::global().raw(), Context::global().stream())); }
+  static void end() {
+    sync();
+    active() = false;
+  }
+  static void commit_async() {
+    it_event*& ev = pending();
+    if (ev == nullptr) check(it_event_create(Context::global().raw(), &ev));
+    check(it_event_record(Context::global().raw(), Context::global().stream(), ev));
+    recorded() = true;
+    active() = false;
+  }
+  static bool is_async_complete() {
+    if (!recorded()) return true;
+    int32_t done = 0;
+    check(it_event_query(Context::global().raw(), pending(), &done));
+    return done != 0;
+  }
+  static void wait_for_completion() {
+    if (!recorded()) return;
+    check(it_event_wait(Context::global().raw(), pending()));
+    recorded() = false;
+  }
+  // Raises it::Error(IT_ERR_TIMEOUT) if a kernel's bounded wait ran out since the last poll.
+  static void poll_device_status() {
+    int32_t st = 0;
+    check(it_attention_status_poll(Context::global().raw(), Context::global().stream(), &st));
+  }
+
+ private:
+  static bool& active() {
+    thread_local bool a = false;
+    return a;
+  }
+  static bool& recorded() {
+    thread_local bool r = false;
+    return r;
+  }
+  static it_event*& pending() {
+    thread_local it_event* e = nullptr;
+    return e;
+  }
+};
+
+// Device buffer + shape + precision (src/tensor.rs:11-15).  view() shares the buffer, like the
+// reference's retained MTLBuffer (src/tensor.rs:183-198).
+class Tensor {
+ public:
+  Tensor() = default;
+  static Tensor zeros(const std::vector<size_t>& shape, Precision p = Precision::FP32) {
+    Tensor t(shape, p);
+    check(it_buf_memset_async(Context::global().raw(), Context::global().stream(), t.ptr(), 0, t.byte_size()));
+    return t;
+  }
+  static Tensor empty(const std::vector<size_t>& shape, Precision p) { return Tensor(shape, p); }
+  static Tensor from_f32_slice(const std::vector<float>& data, const std::vector<size_t>& shape) {
+    Tensor t(shape, Precision::FP32);
+    require(data.size() == t.numel(), "Data length does not match shape");
+    check(it_buf_upload(Context::global().raw(), Context::global().stream(), t.ptr(), data.data(), t.byte_size()));
+    CommandBatch::sync();   // `data` may go away after the call
+    return t;
+  }
+  static Tensor from_f32_as_bf16(const std::vector<float>& data, const std::vector<size_t>& shape) {
+    Tensor t(shape, Precision::BF16);
+    require(data.size() == t.numel(), "Data length does not match shape");
+    std::vector<uint16_t> bits(data.size());
+    for (size_t i = 0; i < data.size(); ++i) bits[i] = f32_to_bf16(data[i]);
+    check(it_buf_upload(Context::global().raw(), Context::global().stream(), t.ptr(), bits.data(), t.byte_size()));
+    CommandBatch::sync();
+    return t;
+  }
+  const std::vector<size_t>& shape() const { return shape_; }
+  Precision precision() const { return precision_; }
+  size_t numel() const {
+    size_t n = 1;
+    for (size_t d : shape_) n *= d;
+    return n;
+  }
+  size_t byte_size() const { return numel() * it::byte_size(precision_); }
+  void* ptr() const { return buf_ ? buf_->dev : nullptr; }
+  // Values on the host as fp32, whatever the storage precision (as_f32_slice, src/tensor.rs:136-148;
+  // the reference aliases unified memory, here the stream is drained and the bytes are copied).
+  std::vector<float> to_host_f32() const {
+    std::vector<float> out(numel());
+    if (numel() == 0) return out;
+    if (precision_ == Precision::FP32) {
+      check(it_buf_download(Context::global().raw(), Context::global().stream(), out.data(), ptr(), byte_size()));
+      CommandBatch::sync();
+    } else {
+      std::vector<uint16_t> bits(numel());
+      check(it_buf_download(Context::global().raw(), Context::global().stream(), bits.data(), ptr(), byte_size()));
+      CommandBatch::sync();
+      for (size_t i = 0; i < bits.size(); ++i) out[i] = bf16_to_f32(bits[i]);
+    }
+    return out;
+  }
+  Tensor view(const std::vector<size_t>& new_shape) const {
+    Tensor t = *this;
+    t.shape_ = new_shape;
+    require(t.numel() == numel(), "Cannot view tensor with a different number of elements");
+    return t;
+  }
+  // Side output of flash_attention: per-row log-sum-exp [B,H,S], fp32 (the reference has none).
+  std::shared_ptr<Tensor> lse;
+
+ private:
+  struct Buf {
+    void* dev = nullptr;
+    ~Buf() {
+      if (dev) it_buf_free(Context::global().raw(), dev);
+    }
+  };
+  Tensor(const std::vector<size_t>& shape, Precision p) : shape_(shape), precision_(p), buf_(std::make_shared<Buf>()) {
+    check(it_buf_alloc(Context::global().raw(), byte_size(), &buf_->dev));
+  }
+  std::vector<size_t> shape_;
+  Precision precision_ = Precision::FP32;
+  std::shared_ptr<Buf> buf_;
+};
+
+inline it_dtype dtype_code(Precision p) { return p == Precision::FP32 ? IT_F32 : IT_BF16; }
+
+// src/ops/flash_attention.rs:76-193
+inline Tensor flash_attention(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
+  require(q.precision() == k.precision() && q.precision() == v.precision(), "Q, K and V must have the same precision");
+  require(q.shape().size() == 4, "Q must be 4D [batch, heads, seq, head_dim]");
+  require(k.shape().size() == 4, "K must be 4D [batch, heads, seq, head_dim]");
+  require(v.shape().size() == 4, "V must be 4D [batch, heads, seq, head_dim]");
+  require(q.shape() == k.shape(), "Q and K must have same shape");
+  require(q.shape() == v.shape(), "Q and V must have same shape");
+  const auto& s = q.shape();
+  require(s[3] <= 128, "head_dim must be <= 128");
+  Tensor out = Tensor::zeros(s, q.precision());
+  out.lse = std::make_shared<Tensor>(Tensor::zeros({s[0], s[1], s[2]}, Precision::FP32));
+  if (s[2] == 0 || s[0] * s[1] == 0) return out;
+  check(it_flash_attention_fwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                               static_cast<int32_t>(s[0]), static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
+                               static_cast<int32_t>(s[3]), causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), out.ptr(),
+                               static_cast<float*>(out.lse->ptr())));
+  return out;
+}
+
+// src/train/helpers.rs:120-193.  The reference takes (grad_output, q, k, v) and is always causal; pass
+// the forward's result (`o`, carrying `o.lse`) to skip re-running the forward.
+inline std::tuple<Tensor, Tensor, Tensor> attention_backward_recompute(const Tensor& grad_output, const Tensor& q,
+                                                                       const Tensor& k, const Tensor& v,
+                                                                       const Tensor* o = nullptr, bool causal = true) {
+  const auto& s = q.shape();
+  require(s.size() == 4, "Q must be 4D [batch, heads, seq, head_dim]");
+  require(grad_output.shape() == s && k.shape() == s && v.shape() == s, "shape mismatch");
+  require(grad_output.precision() == q.precision() && k.precision() == q.precision() && v.precision() == q.precision(),
+          "all tensors must have the same precision");
+  Tensor dq = Tensor::zeros(s, q.precision()), dk = Tensor::zeros(s, q.precision()), dv = Tensor::zeros(s, q.precision());
+  if (s[2] == 0 || s[0] * s[1] == 0) return {dq, dk, dv};
+  Tensor fwd;
+  if (o == nullptr || !o->lse) {
+    fwd = flash_attention(q, k, v, causal);
+    o = &fwd;
+  }
+  size_t ws_bytes = 0;
+  check(it_flash_attention_bwd_workspace_bytes(dtype_code(q.precision()), static_cast<int32_t>(s[0]),
+                                               static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
+                                               static_cast<int32_t>(s[3]), &ws_bytes));
+  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);   // freed after the stream has used it
+  check(it_flash_attention_bwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                               static_cast<int32_t>(s[0]), static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
+                               static_cast<int32_t>(s[3]), causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), o->ptr(),
+                               grad_output.ptr(), static_cast<const float*>(o->lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(),
+                               ws.ptr(), ws_bytes));
+  CommandBatch::sync();   // the scratch goes out of scope here
+  return {dq, dk, dv};
+}
+
+// src/ops/attention.rs:286-377: [batch, seq, heads, head_dim] in and out.  The layout change is done on
+// the host here (the reference does it with transpose kernels around its GEMMs); K/V with another
+// sequence length than Q (allowed there when not causal) is not taken.
+inline Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
+  require(q.shape().size() == 4, "Q must be 4D [batch, seq, heads, dim]");
+  require(k.shape().size() == 4, "K must be 4D [batch, seq, heads, dim]");
+  require(v.shape().size() == 4, "V must be 4D [batch, seq, heads, dim]");
+  require(q.precision() == Precision::FP32 && k.precision() == Precision::FP32 && v.precision() == Precision::FP32,
+          "attention() takes FP32 tensors");
+  const size_t B = q.shape()[0], S = q.shape()[1], H = q.shape()[2], D = q.shape()[3];
+  require(k.shape()[0] == B && v.shape()[0] == B, "Batch size mismatch");
+  require(k.shape()[2] == H && v.shape()[2] == H, "Num heads mismatch");
+  require(k.shape()[3] == D && v.shape()[3] == D, "Head dim mismatch");
+  require(v.shape()[1] == k.shape()[1], "K and V seq_len must match");
+  if (B == 0 || S == 0 || k.shape()[1] == 0) return Tensor::zeros({B, S, H, D}, Precision::FP32);
+  require(k.shape()[1] == S, "attention(): only K/V of the same sequence length as Q are fused");
+  auto swap12 = [&](const std::vector<float>& in, size_t d1, size_t d2) {   // [B,d1,d2,D] -> [B,d2,d1,D]
+    std::vector<float> out(in.size());
+    for (size_t b = 0; b < B; ++b)
+      for (size_t i = 0; i < d1; ++i)
+        for (size_t j = 0; j < d2; ++j)
+          std::memcpy(&out[((b * d2 + j) * d1 + i) * D], &in[((b * d1 + i) * d2 + j) * D], D * sizeof(float));
+    return out;
+  };
+  const Tensor tq = Tensor::from_f32_slice(swap12(q.to_host_f32(), S, H), {B, H, S, D});
+  const Tensor tk = Tensor::from_f32_slice(swap12(k.to_host_f32(), S, H), {B, H, S, D});
+  const Tensor tv = Tensor::from_f32_slice(swap12(v.to_host_f32(), S, H), {B, H, S, D});
+  const Tensor o = flash_attention(tq, tk, tv, causal);
+  return Tensor::from_f32_slice(swap12(o.to_host_f32(), H, S), {B, S, H, D});
+}
+
+}  // namespace it
