@@ -72,11 +72,13 @@ struct BwdParams {
 };
 
 // ------------------------------------------------------------------ (1) prepare
-// One warp per (bh, row): delta and LSE*log2e into the padded arrays.
+// One warp per (bh, row): delta and LSE*log2e into the padded arrays, and the row's slice of the fp32
+// dQ accumulator cleared (saves a separate pass over those 4*D bytes per row).
 template <int D>
 __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       const float* __restrict__ lse, float* __restrict__ lse2_pad,
-                                      float* __restrict__ delta_pad, int S, int S_pad, int BH) {
+                                      float* __restrict__ delta_pad, float* __restrict__ dq_accum, int S, int S_pad,
+                                      int BH) {
   const int lane = threadIdx.x & 31;
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= static_cast<long long>(BH) * S_pad) return;
@@ -90,6 +92,9 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
     return;
   }
   const size_t base = (static_cast<size_t>(bh) * S + s) * D;
+#pragma unroll
+  for (int c = 0; c < D / 128 + (D % 128 ? 1 : 0); ++c)
+    if (c * 128 + lane * 4 < D) reinterpret_cast<float4*>(dq_accum + base)[c * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
   float acc = 0.f;
   if (D == 128) {
     const uint2 a = reinterpret_cast<const uint2*>(o + base)[lane];

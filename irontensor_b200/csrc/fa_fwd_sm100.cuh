@@ -253,12 +253,14 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]), mx2 = __uint_as_float(r[2]),
               mx3 = __uint_as_float(r[3]);
 #pragma unroll
-        for (int i = 4; i < 128; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+        for (int i = 4; i < 124; i += 8) {   // three-input max: two new values per instruction
+          mx0 = fmax3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
         }
+        mx0 = fmax3(mx0, __uint_as_float(r[124]), __uint_as_float(r[125]));
+        mx1 = fmax3(mx1, __uint_as_float(r[126]), __uint_as_float(r[127]));
         const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
         if (j == 0) {
           m_used = m_new;

@@ -252,6 +252,11 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // lo -> low 16 bits (the even element), hi -> high 16 bits; round-to-nearest-even.
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
