@@ -239,7 +239,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const int st = n & 1;
           const uint32_t ph = (n >> 1) & 1;
           const int qi = i0 + n;
-          if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
+          if (!mbar_wait_parked(&q_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(&q_full[st], T::TILE_BYTES + 1024);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_3d(smem + T::SMEM_Q + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[st], b * 64,
@@ -255,7 +255,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                   smem_addr(smem + T::SMEM_DELTA + st * 512)),
               "l"(reinterpret_cast<uint64_t>(prm.delta_pad + row0)), "r"(smem_addr(&q_full[st]))
               : "memory");
-          if (!mbar_wait(do_empty, (n & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
+          if (!mbar_wait_parked(do_empty, (n & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(do_full, T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_3d(smem + T::SMEM_DO + b * T::BLOCK_BYTES, &tmap_do, do_full, b * 64, qi * T::BN, bh);
@@ -314,8 +314,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             umma_ss(tmem_base + T::COL_DQ, sdesc_advance(da, kk * 2048), sdesc_advance(db, kk * 2048), IDESC_DQ,
                     kk > 0);
         };
-        bool ok = mbar_wait(kv_full, 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-        if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+        bool ok = mbar_wait_parked(kv_full, 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+        if (ok) ok = mbar_wait_parked(&q_full[0], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
         if (ok) {
           tc_fence_after();
           issue_st(0);
@@ -323,15 +323,15 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int n = 0; n < n_iter && ok; ++n) {
           const int st = n & 1;
           const uint32_t ph = (n >> 1) & 1;
-          ok = mbar_wait(do_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+          ok = mbar_wait_parked(do_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
           if (!ok) break;
           if (n > 0) {   // dQ(n-1) must have left TMEM before dP^T(n) overwrites those columns
-            ok = mbar_wait(dq_empty, (n - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+            ok = mbar_wait_parked(dq_empty, (n - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
             if (!ok) break;
           }
           tc_fence_after();
           issue_dpt();
-          ok = mbar_wait(p_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+          ok = mbar_wait_parked(p_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
           issue_dv(n == 0);
@@ -339,12 +339,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (n + 1 < n_iter) {
             const int st_n = (n + 1) & 1;
             const uint32_t ph_n = ((n + 1) >> 1) & 1;
-            ok = mbar_wait(&q_full[st_n], ph_n, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+            ok = mbar_wait_parked(&q_full[st_n], ph_n, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
             if (!ok) break;
             tc_fence_after();
             issue_st(st_n);
           }
-          ok = mbar_wait(ds_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+          ok = mbar_wait_parked(ds_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
           issue_dq();
@@ -378,8 +378,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const float* lse_s = reinterpret_cast<const float*>(smem + T::SMEM_LSE + st * 512) + half * 64;
         const float* dl_s = reinterpret_cast<const float*>(smem + T::SMEM_DELTA + st * 512) + half * 64;
         // lse/delta for this query tile ride on the Q barrier
-        ok = mbar_wait(&q_full[st], (n >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-        if (ok) ok = mbar_wait(st_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = mbar_wait_parked(&q_full[st], (n >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+        if (ok) ok = mbar_wait_parked(st_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -420,7 +420,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tc_fence_before();
         mbar_arrive(p_full);
         // phase B: dS^T = P^T o (dP^T - delta), bf16, swizzled into shared memory
-        ok = mbar_wait(dpt_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = mbar_wait_parked(dpt_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -456,7 +456,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         mbar_arrive(ds_full);
       }
       if (ok) {
-        ok = mbar_wait(dkv_done, 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = mbar_wait_parked(dkv_done, 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
@@ -505,7 +505,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint32_t r[D / 32][32];
       int g = 0;   // chunks handled so far
       for (int n = 0; n < n_iter && ok; ++n) {
-        ok = mbar_wait(dq_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = mbar_wait_parked(dq_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -520,7 +520,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const uint32_t use = static_cast<uint32_t>(g >> 1);
           uint8_t* stage = smem + T::SMEM_DQS + buf * T::BLOCK_BYTES;
           // the reduce that read this buffer two chunks ago must be done with it
-          ok = mbar_wait(&dqs_free[buf], (use & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY);
+          ok = mbar_wait_parked(&dqs_free[buf], (use & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           uint8_t* dst = stage + row * 128;
@@ -531,7 +531,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           fence_proxy_async_smem();
           mbar_arrive(&dqs_full[buf]);
           if (issuer) {
-            if (mbar_wait(&dqs_full[buf], use & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX)) {
+            if (mbar_wait_parked(&dqs_full[buf], use & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX)) {
               tma_reduce_add_3d(&tmap_dq, stage, c * 32, (i0 + n) * T::BN, bh);
               bulk_commit_group();
               if (g >= 1) {   // the previous chunk's reduce has read the other buffer: hand it back

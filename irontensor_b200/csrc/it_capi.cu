@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <cmath>
@@ -649,10 +650,12 @@ it_status it_selftest_umma_rate(it_ctx* ctx, it_stream* stream, int32_t variant,
     return fail(IT_ERR_INVALID_ARG, "variant 0..4, ctas 1..1024, iters 1..100000");
   IT_CUDA(cudaSetDevice(ctx->device));
   const int smem = 6 * 128 * 128 + 64;
+  const char* tr = getenv("IT_RATE_TRACE");
+  long long* trace = tr ? reinterpret_cast<long long*>(strtoull(tr, nullptr, 0)) : nullptr;
 #define IT_RATE_CASE(V)                                                                                      \
   case V:                                                                                                    \
     IT_CUDA(cudaFuncSetAttribute(it::umma_rate_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    it::umma_rate_kernel<V><<<ctas, 128, smem, stream->s>>>(iters, ctx->d_status);                           \
+    it::umma_rate_kernel<V><<<ctas, 128, smem, stream->s>>>(iters, ctx->d_status, trace);                           \
     break;
   switch (variant) {
     IT_RATE_CASE(0)
