@@ -109,6 +109,23 @@ it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype,
                                  const void* v, const void* o, const void* d_o, const float* lse, void* dq,
                                  void* dk, void* dv, void* workspace, size_t workspace_bytes);
 
+/* attention(q, k, v, causal) on [batch, seq, heads, head_dim] tensors (src/ops/attention.rs:286-377), and
+ * its backward in the same layout.  The reference gets from this layout to the flash-attention one and
+ * back with transpose kernels (src/ops/transpose.rs:277-395; three before and one after each forward,
+ * src/train/forward.rs:125-127,141; one before and three after each backward, src/train/backward.rs:102,
+ * 114-116).  Here the kernels read and write the [B,S,H,D] tensors in place through strided TMA
+ * descriptors, so those copies disappear.  Same math, dispatch, workspace size
+ * (it_flash_attention_bwd_workspace_bytes with the same B, H, S, D) and error codes as the [B,H,S,D] entry
+ * points; lse stays [batch, heads, seq].  K/V with another sequence length than Q (which the reference
+ * allows when not causal) are not taken. */
+it_status it_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq, int32_t heads,
+                           int32_t head_dim, int32_t causal, const void* q, const void* k, const void* v, void* o,
+                           float* lse);
+it_status it_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq, int32_t heads,
+                           int32_t head_dim, int32_t causal, const void* q, const void* k, const void* v, const void* o,
+                           const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
+                           size_t workspace_bytes);
+
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)
  *

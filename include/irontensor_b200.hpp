@@ -249,35 +249,49 @@ inline std::tuple<Tensor, Tensor, Tensor> attention_backward_recompute(const Ten
   return {dq, dk, dv};
 }
 
-// src/ops/attention.rs:286-377: [batch, seq, heads, head_dim] in and out.  The layout change is done on
-// the host here (the reference does it with transpose kernels around its GEMMs); K/V with another
-// sequence length than Q (allowed there when not causal) is not taken.
+// src/ops/attention.rs:286-377: [batch, seq, heads, head_dim] in and out.  The kernels read and write
+// this layout in place, so the transposes the reference runs around its GEMMs are gone; K/V with
+// another sequence length than Q (allowed there when not causal) is not taken.  The result carries
+// `.lse` ([batch, heads, seq]) for attention_backward.
 inline Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
   require(q.shape().size() == 4, "Q must be 4D [batch, seq, heads, dim]");
   require(k.shape().size() == 4, "K must be 4D [batch, seq, heads, dim]");
   require(v.shape().size() == 4, "V must be 4D [batch, seq, heads, dim]");
-  require(q.precision() == Precision::FP32 && k.precision() == Precision::FP32 && v.precision() == Precision::FP32,
-          "attention() takes FP32 tensors");
+  require(q.precision() == k.precision() && q.precision() == v.precision(), "Q, K and V must have the same precision");
   const size_t B = q.shape()[0], S = q.shape()[1], H = q.shape()[2], D = q.shape()[3];
   require(k.shape()[0] == B && v.shape()[0] == B, "Batch size mismatch");
   require(k.shape()[2] == H && v.shape()[2] == H, "Num heads mismatch");
   require(k.shape()[3] == D && v.shape()[3] == D, "Head dim mismatch");
   require(v.shape()[1] == k.shape()[1], "K and V seq_len must match");
-  if (B == 0 || S == 0 || k.shape()[1] == 0) return Tensor::zeros({B, S, H, D}, Precision::FP32);
+  Tensor out = Tensor::zeros({B, S, H, D}, q.precision());
+  out.lse = std::make_shared<Tensor>(Tensor::zeros({B, H, S}, Precision::FP32));
+  if (B == 0 || S == 0 || k.shape()[1] == 0) return out;
   require(k.shape()[1] == S, "attention(): only K/V of the same sequence length as Q are fused");
-  auto swap12 = [&](const std::vector<float>& in, size_t d1, size_t d2) {   // [B,d1,d2,D] -> [B,d2,d1,D]
-    std::vector<float> out(in.size());
-    for (size_t b = 0; b < B; ++b)
-      for (size_t i = 0; i < d1; ++i)
-        for (size_t j = 0; j < d2; ++j)
-          std::memcpy(&out[((b * d2 + j) * d1 + i) * D], &in[((b * d1 + i) * d2 + j) * D], D * sizeof(float));
-    return out;
-  };
-  const Tensor tq = Tensor::from_f32_slice(swap12(q.to_host_f32(), S, H), {B, H, S, D});
-  const Tensor tk = Tensor::from_f32_slice(swap12(k.to_host_f32(), S, H), {B, H, S, D});
-  const Tensor tv = Tensor::from_f32_slice(swap12(v.to_host_f32(), S, H), {B, H, S, D});
-  const Tensor o = flash_attention(tq, tk, tv, causal);
-  return Tensor::from_f32_slice(swap12(o.to_host_f32(), H, S), {B, S, H, D});
+  check(it_attention_fwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                         static_cast<int32_t>(B), static_cast<int32_t>(S), static_cast<int32_t>(H), static_cast<int32_t>(D),
+                         causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), out.ptr(), static_cast<float*>(out.lse->ptr())));
+  return out;
+}
+
+// Gradients for attention(), all tensors [batch, seq, heads, head_dim]; `o` is attention()'s result.
+inline std::tuple<Tensor, Tensor, Tensor> attention_backward(const Tensor& grad_output, const Tensor& q, const Tensor& k,
+                                                             const Tensor& v, const Tensor& o, bool causal = true) {
+  const auto& s = q.shape();
+  require(s.size() == 4 && grad_output.shape() == s && k.shape() == s && v.shape() == s && o.shape() == s, "shape mismatch");
+  require(static_cast<bool>(o.lse), "o must come from attention()");
+  Tensor dq = Tensor::zeros(s, q.precision()), dk = Tensor::zeros(s, q.precision()), dv = Tensor::zeros(s, q.precision());
+  if (s[1] == 0 || s[0] * s[2] == 0) return {dq, dk, dv};
+  size_t ws_bytes = 0;
+  check(it_flash_attention_bwd_workspace_bytes(dtype_code(q.precision()), static_cast<int32_t>(s[0]),
+                                               static_cast<int32_t>(s[2]), static_cast<int32_t>(s[1]),
+                                               static_cast<int32_t>(s[3]), &ws_bytes));
+  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  check(it_attention_bwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                         static_cast<int32_t>(s[0]), static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
+                         static_cast<int32_t>(s[3]), causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), o.ptr(), grad_output.ptr(),
+                         static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws.ptr(), ws_bytes));
+  CommandBatch::sync();   // the scratch goes out of scope here
+  return {dq, dk, dv};
 }
 
 }  // namespace it

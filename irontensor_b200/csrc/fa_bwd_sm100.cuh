@@ -57,6 +57,7 @@ struct BwdTraits {
 };
 
 struct BwdParams {
+  ptx::TensorStrides st;   // layout of q, k, v, o, dO and of dq, dk, dv
   const float* lse2_pad;   // [BH, S_pad] LSE * log2(e), +inf in the padding
   const float* delta_pad;  // [BH, S_pad] rowsum(dO*O), 0 in the padding
   float* dq_accum;         // [BH, S, D] fp32, zeroed by the caller
@@ -78,7 +79,7 @@ template <int D>
 __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       const float* __restrict__ lse, float* __restrict__ lse2_pad,
                                       float* __restrict__ delta_pad, float* __restrict__ dq_accum, int S, int S_pad,
-                                      int BH) {
+                                      int BH, ptx::TensorStrides st) {
   const int lane = threadIdx.x & 31;
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= static_cast<long long>(BH) * S_pad) return;
@@ -91,10 +92,11 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
     }
     return;
   }
-  const size_t base = (static_cast<size_t>(bh) * S + s) * D;
+  const size_t base = static_cast<size_t>(st.slice(bh) + static_cast<long long>(s) * st.row);
+  float* acc_row = dq_accum + (static_cast<size_t>(bh) * S + s) * D;   // the accumulator is always [BH, S, D]
 #pragma unroll
   for (int c = 0; c < D / 128 + (D % 128 ? 1 : 0); ++c)
-    if (c * 128 + lane * 4 < D) reinterpret_cast<float4*>(dq_accum + base)[c * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c * 128 + lane * 4 < D) reinterpret_cast<float4*>(acc_row)[c * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
   float acc = 0.f;
   if (D == 128) {
     const uint2 a = reinterpret_cast<const uint2*>(o + base)[lane];
@@ -123,14 +125,19 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
 
 // ------------------------------------------------------------------ (3) finish
 __global__ void fa_bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq,
-                                     size_t n_vec4, float scale) {
+                                     size_t n_vec4, float scale, int S, int D, ptx::TensorStrides st) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_vec4) return;
   const float4 v = reinterpret_cast<const float4*>(dq_accum)[i];
   uint2 w;
   w.x = ptx::pack_bf16(v.x * scale, v.y * scale);
   w.y = ptx::pack_bf16(v.z * scale, v.w * scale);
-  reinterpret_cast<uint2*>(dq)[i] = w;
+  const size_t e = i * 4;                       // element index in the [BH, S, D] accumulator
+  const size_t row = e / D;
+  const int d = static_cast<int>(e - row * D);
+  const int bh = static_cast<int>(row / S);
+  const int s_ = static_cast<int>(row - static_cast<size_t>(bh) * S);
+  *reinterpret_cast<uint2*>(dq + st.slice(bh) + static_cast<long long>(s_) * st.row + d) = w;
 }
 
 // ------------------------------------------------------------------ (2) main kernel
@@ -171,6 +178,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int n_k_tiles = (S + T::BM - 1) / T::BM;
   const int bh = static_cast<int>(blockIdx.x) / n_k_tiles;
   const int kt = static_cast<int>(blockIdx.x) % n_k_tiles;
+  const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
   const int i0 = prm.causal ? kt : 0;
   const int n_iter = n_q_tiles - i0;
 
@@ -232,8 +240,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         prefetch_tensormap(&tmap_dq);
         mbar_arrive_expect_tx(kv_full, 2 * T::TILE_BYTES);
         for (int b = 0; b < T::NBLK; ++b) {
-          tma_load_3d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, bh);
-          tma_load_3d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, bh);
+          tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, hd, bt);
+          tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, hd, bt);
         }
         for (int n = 0; n < n_iter; ++n) {
           const int st = n & 1;
@@ -242,8 +250,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!mbar_wait_parked(&q_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(&q_full[st], T::TILE_BYTES + 1024);
           for (int b = 0; b < T::NBLK; ++b)
-            tma_load_3d(smem + T::SMEM_Q + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[st], b * 64,
-                        qi * T::BN, bh);
+            tma_load_4d(smem + T::SMEM_Q + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[st], b * 64,
+                        qi * T::BN, hd, bt);
           const size_t row0 = static_cast<size_t>(bh) * prm.S_pad + static_cast<size_t>(qi) * T::BN;
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(
@@ -258,7 +266,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!mbar_wait_parked(do_empty, (n & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(do_full, T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
-            tma_load_3d(smem + T::SMEM_DO + b * T::BLOCK_BYTES, &tmap_do, do_full, b * 64, qi * T::BN, bh);
+            tma_load_4d(smem + T::SMEM_DO + b * T::BLOCK_BYTES, &tmap_do, do_full, b * 64, qi * T::BN, hd, bt);
         }
       }
     } else if (warp == 1) {
@@ -463,8 +471,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // each math group writes one half of the head dimension of its key row's dV and dK
         tc_fence_after();
         constexpr int HC = D / 2;
-        __nv_bfloat16* dv_row = prm.dv + (static_cast<size_t>(bh) * S + k_row) * D + half * HC;
-        __nv_bfloat16* dk_row = prm.dk + (static_cast<size_t>(bh) * S + k_row) * D + half * HC;
+        const long long out_off = prm.st.slice(bh) + static_cast<long long>(k_row) * prm.st.row + half * HC;
+        __nv_bfloat16* dv_row = prm.dv + out_off;
+        __nv_bfloat16* dk_row = prm.dk + out_off;
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           const uint32_t col = (which ? T::COL_DK : T::COL_DV) + half * HC;

@@ -43,7 +43,8 @@ struct FwdTraits {
 };
 
 struct FwdParams {
-  __nv_bfloat16* o;     // [BH, S, D]
+  ptx::TensorStrides st; // layout of q, k, v and o
+  __nv_bfloat16* o;     // output, same layout as the inputs
   float* lse;           // [BH, S] or null
   int* status;          // device status word
   int S;
@@ -81,6 +82,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // tiles they all stream stay in L2.  Within a slice the last query tiles (most keys) go first.
   const int bh = static_cast<int>(blockIdx.x) / n_pairs;
   const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) % n_pairs;
+  const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
   int n_kv[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -139,8 +141,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (n_kv[t] == 0) continue;
           mbar_arrive_expect_tx(&q_full[t], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
-            tma_load_3d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
-                        (2 * pair + t) * T::BM, bh);
+            tma_load_4d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
+                        (2 * pair + t) * T::BM, hd, bt);
         }
         for (int j = 0; j < n_iter; ++j) {
           const int st = j % T::STAGES;
@@ -148,13 +150,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
-            tma_load_3d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
-                        j * T::BN, bh);
+            tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
+                        j * T::BN, hd, bt);
           if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
-            tma_load_3d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
-                        j * T::BN, bh);
+            tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
+                        j * T::BN, hd, bt);
         }
       }
     } else if (warp == 1) {
@@ -316,7 +318,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (ok) {
         tc_fence_after();
         const float inv_l = 1.0f / l_sum;
-        __nv_bfloat16* orow = prm.o + (static_cast<size_t>(bh) * S + q_row) * D;
+        __nv_bfloat16* orow = prm.o + prm.st.slice(bh) + static_cast<long long>(q_row) * prm.st.row;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) tmem_ld_x32(t_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
         tmem_wait_ld();

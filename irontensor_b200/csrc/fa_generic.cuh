@@ -15,6 +15,8 @@
 #include <cuda_bf16.h>
 #include <cstdint>
 
+#include "layout.cuh"
+
 namespace it {
 
 __device__ __forceinline__ float g_ex2(float x) {
@@ -43,7 +45,8 @@ template <> __device__ __forceinline__ void st_from_f32<__nv_bfloat16>(__nv_bflo
 template <typename ST, int DP>
 __global__ void __launch_bounds__(256)
 fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
-                      ST* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2) {
+                      ST* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
+                      TensorStrides st) {
   constexpr int BM = 64;
   constexpr int BN = (DP >= 128) ? 32 : 64;
   constexpr int NCH = DP / 16;              // float4 chunks per thread
@@ -58,7 +61,8 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   const int bh = blockIdx.y;
   const int row = rt * BM + r_local;
   const bool row_ok = row < S;
-  const size_t base = static_cast<size_t>(bh) * S * D;
+  const size_t base = static_cast<size_t>(st.slice(bh));
+  const size_t RS = static_cast<size_t>(st.row);
 
   float4 qv[NCH], acc[NCH];
 #pragma unroll
@@ -67,7 +71,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
     float tmp[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-      tmp[e] = (row_ok && d0 + e < D) ? ld_as_f32(q + base + static_cast<size_t>(row) * D + d0 + e) : 0.f;
+      tmp[e] = (row_ok && d0 + e < D) ? ld_as_f32(q + base + static_cast<size_t>(row) * RS + d0 + e) : 0.f;
     qv[j] = make_float4(tmp[0], tmp[1], tmp[2], tmp[3]);
     acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
@@ -81,7 +85,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
     for (int i = tid; i < BN * DP; i += 256) {
       const int kk = i / DP, d = i % DP;
       const bool okk = (kk < nk) && (d < D);
-      const size_t g = base + static_cast<size_t>(k0 + kk) * D + d;
+      const size_t g = base + static_cast<size_t>(k0 + kk) * RS + d;
       sK[i] = okk ? ld_as_f32(k + g) : 0.f;
       sV[i] = okk ? ld_as_f32(v + g) : 0.f;
     }
@@ -143,7 +147,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
       const float tmp[4] = {acc[j].x * inv, acc[j].y * inv, acc[j].z * inv, acc[j].w * inv};
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        if (d0 + e < D) st_from_f32(o + base + static_cast<size_t>(row) * D + d0 + e, tmp[e]);
+        if (d0 + e < D) st_from_f32(o + base + static_cast<size_t>(row) * RS + d0 + e, tmp[e]);
     }
     if (lse != nullptr && t4 == 0)
       lse[static_cast<size_t>(bh) * S + row] = (m_run + g_lg2(l_run)) * 0.6931471805599453f;
@@ -162,7 +166,8 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
 template <int NJ>
 __global__ void __launch_bounds__(128)
 fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                       float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2) {
+                       float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
+                       TensorStrides st) {
   constexpr int RB = 16, RW = 4, TK = 32;
   extern __shared__ __align__(16) float sm[];
   const int DS = D + 4;                       // padded row stride (floats)
@@ -176,7 +181,8 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
   const int rb = n_rb - 1 - static_cast<int>(blockIdx.x);    // longest rows first
   const int bh = blockIdx.y;
   const int r0 = rb * RB;
-  const size_t base = static_cast<size_t>(bh) * S * D;
+  const size_t base = static_cast<size_t>(st.slice(bh));
+  const size_t RS = static_cast<size_t>(st.row);
   const int k_end_cta = causal ? min(S, r0 + RB) : S;
   const int n_tiles = (k_end_cta + TK - 1) / TK;
 
@@ -189,7 +195,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
       float* pk = dk + key * DS + 4 * c;
       float* pv = dv + key * DS + 4 * c;
       if (k0 + key < k_end_cta) {
-        const size_t g = base + static_cast<size_t>(k0 + key) * D + 4 * c;
+        const size_t g = base + static_cast<size_t>(k0 + key) * RS + 4 * c;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(pk))), "l"(k + g));
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(pv))), "l"(v + g));
       } else {   // rows past the end: zeros, so that 0 * V stays 0
@@ -204,7 +210,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
   for (int idx = tid; idx < RB * nd4; idx += 128) {
     const int rr = idx / nd4, c = idx - rr * nd4;
     float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r0 + rr < S) val = reinterpret_cast<const float4*>(q + base + static_cast<size_t>(r0 + rr) * D)[c];
+    if (r0 + rr < S) val = reinterpret_cast<const float4*>(q + base + static_cast<size_t>(r0 + rr) * RS)[c];
     reinterpret_cast<float4*>(sQ + rr * D)[c] = val;
   }
 
@@ -299,7 +305,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
 #pragma unroll
       for (int jj = 0; jj < NJ; ++jj) {
         const int d = lane + 32 * jj;
-        if (d < D) o[base + static_cast<size_t>(row) * D + d] = acc[w][jj] * inv;
+        if (d < D) o[base + static_cast<size_t>(row) * RS + d] = acc[w][jj] * inv;
       }
       if (lse != nullptr && lane == 0)
         lse[static_cast<size_t>(bh) * S + row] = (m_run[w] + g_lg2(l_run[w])) * 0.6931471805599453f;
@@ -310,14 +316,16 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
 // delta[bh, s] = sum_d dO * O, one warp per row.
 template <typename ST>
 __global__ void fa_bwd_generic_delta_kernel(const ST* __restrict__ o, const ST* __restrict__ d_o,
-                                            float* __restrict__ delta, long long rows, int D) {
+                                            float* __restrict__ delta, long long rows, int S, int D, TensorStrides st) {
   const int lane = threadIdx.x & 31;
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
+  const int bh = static_cast<int>(row / S);
+  const long long off = st.slice(bh) + (row - static_cast<long long>(bh) * S) * st.row;
   float a = 0.f;
-  for (int d = lane; d < D; d += 32) a = fmaf(ld_as_f32(o + row * D + d), ld_as_f32(d_o + row * D + d), a);
+  for (int d = lane; d < D; d += 32) a = fmaf(ld_as_f32(o + off + d), ld_as_f32(d_o + off + d), a);
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+  for (int off2 = 16; off2 > 0; off2 >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off2);
   if (lane == 0) delta[row] = a;
 }
 
@@ -329,12 +337,13 @@ __global__ void __launch_bounds__(128)
 fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
                       const ST* __restrict__ d_o, const float* __restrict__ lse, const float* __restrict__ delta,
                       ST* __restrict__ dq, ST* __restrict__ dk, ST* __restrict__ dv, int S, int D, int causal,
-                      float scale) {
+                      float scale, TensorStrides st) {
   const int lane = threadIdx.x & 31;
   const int r = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5);
   const int bh = blockIdx.y;
   if (r >= S) return;
-  const size_t base = static_cast<size_t>(bh) * S * D;
+  const size_t base = static_cast<size_t>(st.slice(bh));
+  const size_t RS = static_cast<size_t>(st.row);
   const float* lse_h = lse + static_cast<size_t>(bh) * S;
   const float* dl_h = delta + static_cast<size_t>(bh) * S;
   float a0[4], a1[4], g0[4], g1[4];
@@ -342,7 +351,7 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   for (int j = 0; j < 4; ++j) {
     const int d = lane + 32 * j;
     const bool in = d < D;
-    const size_t off = base + static_cast<size_t>(r) * D + d;
+    const size_t off = base + static_cast<size_t>(r) * RS + d;
     if (MODE == 0) {
       a0[j] = in ? ld_as_f32(q + off) : 0.f;     // q_i
       a1[j] = in ? ld_as_f32(d_o + off) : 0.f;   // dO_i
@@ -364,7 +373,7 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
     for (int j = 0; j < 4; ++j) {
       const int d = lane + 32 * j;
       const bool in = d < D;
-      const size_t off = base + static_cast<size_t>(x) * D + d;
+      const size_t off = base + static_cast<size_t>(x) * RS + d;
       if (MODE == 0) {
         b0[j] = in ? ld_as_f32(k + off) : 0.f;   // k_x
         b1[j] = in ? ld_as_f32(v + off) : 0.f;   // v_x
@@ -400,7 +409,7 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   for (int j = 0; j < 4; ++j) {
     const int d = lane + 32 * j;
     if (d < D) {
-      const size_t off = base + static_cast<size_t>(r) * D + d;
+      const size_t off = base + static_cast<size_t>(r) * RS + d;
       if (MODE == 0) {
         st_from_f32(dq + off, g0[j] * scale);
       } else {

@@ -66,20 +66,27 @@ struct it_event {
 
 namespace {
 
-// [BH, S, D] bf16 row-major viewed as a 3-D tensor (d innermost); one box = 128 rows x 64 columns
-// of one head, written to shared memory with the 128-byte swizzle.  Rows past S read as zero.
-it_status make_tmap(it_ctx* ctx, CUtensorMap* map, const void* base, int64_t BH, int64_t S, int64_t D,
-                    int box_rows) {
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(BH)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(S) * D * 2};
-  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+// A bf16 attention tensor viewed by TMA as a 4-D tensor (head_dim, seq, heads, batch) with the
+// layout's strides; one box = 128 rows x 64 columns of one (batch, head) slice, written to shared
+// memory with the 128-byte swizzle.  Rows past `seq` read as zero.
+it_status make_tmap(it_ctx* ctx, CUtensorMap* map, const void* base, int64_t B, int64_t H, int64_t S, int64_t D,
+                    const it::TensorStrides& st, int box_rows) {
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st.row) * 2, static_cast<cuuint64_t>(st.head) * 2,
+                                 static_cast<cuuint64_t>(st.batch) * 2};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(IT_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
   return IT_OK;
 }
+
+// [B,H,S,D] (flash_attention) and [B,S,H,D] (attention) as strides in elements.
+it::TensorStrides strides_bhsd(int64_t H, int64_t S, int64_t D) { return it::TensorStrides{D, S * D, H * S * D, static_cast<int>(H)}; }
+it::TensorStrides strides_bshd(int64_t H, int64_t S, int64_t D) { return it::TensorStrides{H * D, D, S * H * D, static_cast<int>(H)}; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -102,7 +109,7 @@ int round_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128; }
 
 template <typename ST>
 void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
-                        const void* v, void* o, float* lse) {
+                        const void* v, void* o, float* lse, const it::TensorStrides& st) {
   const float scale = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;   // exp2 domain
   const dim3 grid((S + 63) / 64, BH);
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
@@ -114,9 +121,9 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
                 *vf = reinterpret_cast<const float*>(v);
     float* of = reinterpret_cast<float*>(o);
     if (D <= 32) {
-      it::fa_fwd_rows_f32_kernel<1><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale);
+      it::fa_fwd_rows_f32_kernel<1><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st);
     } else if (D <= 64) {
-      it::fa_fwd_rows_f32_kernel<2><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale);
+      it::fa_fwd_rows_f32_kernel<2><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st);
     } else {
       static bool attr_set[16] = {};
       if (!attr_set[ctx->device & 15]) {
@@ -124,16 +131,16 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
                              (16 * 128 + 4 * 32 * 132 + 512) * 4);
         attr_set[ctx->device & 15] = true;
       }
-      it::fa_fwd_rows_f32_kernel<4><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale);
+      it::fa_fwd_rows_f32_kernel<4><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st);
     }
     ctx->launches += 1;
     return;
   }
   switch (round_dp(D)) {
-    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
-    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
-    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
-    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale); break;
+    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
+    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
+    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
+    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
   }
   ctx->launches += 1;
 }
@@ -141,35 +148,37 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
 template <typename ST>
 void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
                         const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-                        float* delta) {
+                        float* delta, const it::TensorStrides& st) {
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
   const ST *oo = static_cast<const ST*>(o), *dd = static_cast<const ST*>(d_o);
   const long long rows = static_cast<long long>(BH) * S;
-  it::fa_bwd_generic_delta_kernel<ST><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(oo, dd, delta, rows, D);
+  it::fa_bwd_generic_delta_kernel<ST><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(oo, dd, delta, rows, S, D, st);
   const dim3 grid((S + 3) / 4, BH);
   it::fa_bwd_generic_kernel<ST, 0><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq),
-                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale);
+                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale, st);
   it::fa_bwd_generic_kernel<ST, 1><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq),
-                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale);
+                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale, st);
   ctx->launches += 3;
 }
 
 template <int D>
-it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causal, const void* q, const void* k,
-                           const void* v, void* o, float* lse) {
+it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
+                           const void* v, void* o, float* lse, const it::TensorStrides& stv) {
+  const int BH = B * H;
   using T = it::FwdTraits<D>;
   CUtensorMap mq, mk, mv;
   it_status st;
-  if ((st = make_tmap(ctx, &mq, q, BH, S, D, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mk, k, BH, S, D, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mv, v, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, k, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, v, B, H, S, D, stv, 128)) != IT_OK) return st;
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(it::fa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
   }
   it::FwdParams p;
+  p.st = stv;
   p.o = static_cast<__nv_bfloat16*>(o);
   p.lse = lse;
   p.status = ctx->d_status;
@@ -212,16 +221,17 @@ BwdWorkspace bwd_workspace_layout(it_dtype dtype, int64_t BH, int64_t S, int64_t
 }
 
 template <int D>
-it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causal, const void* q, const void* k,
+it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk,
-                           void* dv, uint8_t* ws, const BwdWorkspace& w) {
+                           void* dv, uint8_t* ws, const BwdWorkspace& w, const it::TensorStrides& stv) {
+  const int BH = B * H;
   using T = it::BwdTraits<D>;
   CUtensorMap mq, mk, mv, mdo;
   it_status st;
-  if ((st = make_tmap(ctx, &mq, q, BH, S, D, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mk, k, BH, S, D, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mv, v, BH, S, D, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mdo, d_o, BH, S, D, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, k, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, v, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mdo, d_o, B, H, S, D, stv, 128)) != IT_OK) return st;
   // fp32 dQ accumulator [BH, S, D]: boxes of 32 columns x 128 rows for the TMA reduce-add
   CUtensorMap mdq;
   {
@@ -246,8 +256,9 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causa
   const long long rows_pad = static_cast<long long>(BH) * w.S_pad;
   it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad + 7) / 8), 256, 0, s>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, dq_accum, S,
-      w.S_pad, BH);
+      w.S_pad, BH, stv);
   it::BwdParams p;
+  p.st = stv;
   p.lse2_pad = lse2;
   p.delta_pad = delta;
   p.dq_accum = dq_accum;
@@ -269,7 +280,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int BH, int S, int causa
   }
   const size_t n4 = n_dq / 4;
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
-      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale);
+      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, stv);
   ctx->launches += 3;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -469,27 +480,39 @@ it_status it_buf_memset_async(it_ctx* ctx, it_stream* stream, void* dev, int val
   return IT_OK;
 }
 
-it_status it_flash_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
-                                 int32_t D, int32_t causal, const void* q, const void* k, const void* v, void* o,
-                                 float* lse) {
+static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
+                                    int32_t D, int32_t causal, const void* q, const void* k, const void* v, void* o,
+                                    float* lse, bool bshd) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
   const int BH = B * H;
-  if (S == 0 || BH == 0) return IT_OK;   // src/ops/flash_attention.rs:102-104
+  if (S == 0 || BH == 0) return IT_OK;   // src/ops/flash_attention.rs:102-104, src/ops/attention.rs:313-315
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
     return fail(IT_ERR_ALIGNMENT, "q, k, v and o must be 16-byte aligned");
   IT_CUDA(cudaSetDevice(ctx->device));
+  const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
   if (use_sm100_path(dtype, S, D)) {
-    return D == 128 ? launch_fwd_sm100<128>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, lse)
-                    : launch_fwd_sm100<64>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, lse);
+    return D == 128 ? launch_fwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv)
+                    : launch_fwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv);
   }
   if (dtype == IT_F32)
-    launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse);
+    launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv);
   else
-    launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse);
+    launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv);
   IT_CUDA(cudaGetLastError());
   return IT_OK;
+}
+
+it_status it_flash_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
+                                 int32_t D, int32_t causal, const void* q, const void* k, const void* v, void* o,
+                                 float* lse) {
+  return attention_fwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, lse, false);
+}
+
+it_status it_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H, int32_t D,
+                           int32_t causal, const void* q, const void* k, const void* v, void* o, float* lse) {
+  return attention_fwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, lse, true);
 }
 
 it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int32_t H, int32_t S, int32_t D,
@@ -502,10 +525,10 @@ it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int3
   return IT_OK;
 }
 
-it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
-                                 int32_t D, int32_t causal, const void* q, const void* k, const void* v, const void* o,
-                                 const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
-                                 size_t workspace_bytes) {
+static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
+                                    int32_t D, int32_t causal, const void* q, const void* k, const void* v,
+                                    const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                                    void* workspace, size_t workspace_bytes, bool bshd) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
   const int BH = B * H;
@@ -523,17 +546,34 @@ it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype,
     return fail(IT_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
   IT_CUDA(cudaSetDevice(ctx->device));
   uint8_t* ws = static_cast<uint8_t*>(workspace);
+  const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
   if (use_sm100_path(dtype, S, D)) {
-    return D == 128 ? launch_bwd_sm100<128>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w)
-                    : launch_bwd_sm100<64>(ctx, stream->s, BH, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w);
+    return D == 128
+               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv)
+               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv);
   }
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   if (dtype == IT_F32)
-    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta);
+    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv);
   else
-    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta);
+    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv);
   IT_CUDA(cudaGetLastError());
   return IT_OK;
+}
+
+it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
+                                 int32_t D, int32_t causal, const void* q, const void* k, const void* v, const void* o,
+                                 const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
+                                 size_t workspace_bytes) {
+  return attention_bwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
+                            workspace_bytes, false);
+}
+
+it_status it_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H, int32_t D,
+                           int32_t causal, const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                           const float* lse, void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes) {
+  return attention_bwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
+                            workspace_bytes, true);
 }
 
 // Scratch for it_flash_attention_bwd_noalloc: part of the module image on every GPU that loads it.
@@ -623,8 +663,8 @@ it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, cons
   IT_CUDA(cudaSetDevice(ctx->device));
   CUtensorMap ma, mb;
   it_status st;
-  if ((st = make_tmap(ctx, &ma, a_bf16, 1, 128, 128, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mb, b_bf16, 1, 128, 128, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &ma, a_bf16, 1, 1, 128, 128, strides_bhsd(1, 128, 128), 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mb, b_bf16, 1, 1, 128, 128, strides_bhsd(1, 128, 128), 128)) != IT_OK) return st;
   const int smem = 4 * 128 * 128 + 64;
   const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(a_bf16);
 #define IT_SELFTEST_CASE(V)                                                                                     \

@@ -54,8 +54,8 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const uint32_t bytes = (VARIANT == 0 ? 4 : 2) * BLOCK_BYTES;
       mbar_arrive_expect_tx(load_full, bytes);
       for (int b = 0; b < 2; ++b) {
-        if (VARIANT == 0) tma_load_3d(sA + b * BLOCK_BYTES, &tmap_a, load_full, b * 64, 0, 0);
-        tma_load_3d(sB + b * BLOCK_BYTES, &tmap_b, load_full, b * 64, 0, 0);
+        if (VARIANT == 0) tma_load_4d(sA + b * BLOCK_BYTES, &tmap_a, load_full, b * 64, 0, 0, 0);
+        tma_load_4d(sB + b * BLOCK_BYTES, &tmap_b, load_full, b * 64, 0, 0, 0);
       }
     }
     if (VARIANT == 1) {   // row `tid` of A, packed bf16 pairs, into TMEM columns [128,192)

@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "layout.cuh"
+
 namespace it {
 
 // Device-side status codes written to the context's status word (host reads them after a sync).
@@ -137,6 +139,17 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3)
+      : "memory");
+}
+
+using it::TensorStrides;
 
 // Adds a shared-memory tile (fp32, laid out as the tensor map's box) into global memory; the
 // reduction is done by the memory system on whole lines.  Rows outside the tensor are dropped.

@@ -286,6 +286,17 @@ class raw:
         _lib.check(c.lib.it_flash_attention_fwd(c.handle, c.stream(), dtype, B, H, S, D, int(causal), q, k, v, o, lse))
 
     @staticmethod
+    def fwd_bshd(dtype, B, S, H, D, causal, q, k, v, o, lse, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_fwd(c.handle, c.stream(), dtype, B, S, H, D, int(causal), q, k, v, o, lse))
+
+    @staticmethod
+    def bwd_bshd(dtype, B, S, H, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, ws, ws_bytes, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_bwd(c.handle, c.stream(), dtype, B, S, H, D, int(causal), q, k, v, o, d_o, lse,
+                                          dq, dk, dv, ws, ws_bytes))
+
+    @staticmethod
     def bwd_workspace_bytes(dtype, B, H, S, D):
         n = ctypes.c_size_t()
         _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))
@@ -344,8 +355,11 @@ def flash_attention(q, k, v, causal):
 def attention(q, k, v, causal):
     """Scaled dot-product attention on [batch, seq, heads, head_dim] (src/ops/attention.rs:286-377).
 
-    Same math as flash_attention; the layout change is done around the fused kernel.  The
-    reference lets K/V have another sequence length when not causal; that case is not taken here."""
+    Same math as flash_attention.  The kernels read and write this layout in place (strided TMA
+    descriptors), so the transposes the reference runs around its attention are gone.  Accepts FP32
+    like the reference, and BF16.  The result carries `.lse` ([batch, heads, seq]) for
+    attention_backward.  The reference lets K/V have another sequence length when not causal; that
+    case is not taken here."""
     p = q.precision()
     assert k.precision() is p and v.precision() is p
     qs, ks, vs = q.shape(), k.shape(), v.shape()
@@ -361,12 +375,31 @@ def attention(q, k, v, causal):
         return Tensor.zeros([B, Sq, H, D], p)
     if ks[1] != Sq:
         raise NotImplementedError("attention(): K/V sequence length differs from Q's; only self-attention is fused")
+    out = Tensor.empty([B, Sq, H, D], p)
+    out.lse = Tensor.empty([B, H, Sq], Precision.FP32)
+    raw.fwd_bshd(_dtype_code(p), B, Sq, H, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                 out.lse.data_ptr())
+    return out
 
-    def to_bhsd(t):
-        return Tensor(t.torch().permute(0, 2, 1, 3).contiguous().view(-1), [B, H, Sq, D], p)
 
-    o = flash_attention(to_bhsd(q), to_bhsd(k), to_bhsd(v), causal)
-    return Tensor(o.torch().permute(0, 2, 1, 3).contiguous().view(-1), [B, Sq, H, D], p)
+def attention_backward(grad_output, q, k, v, o, causal=True):
+    """(dQ, dK, dV) for attention(): every tensor is [batch, seq, heads, head_dim]; `o` is attention()'s
+    result (with its `.lse`).  The layout-fused counterpart of attention_backward_recompute: the reference
+    transposes the gradient in and the three gradients out (src/train/backward.rs:102,114-116)."""
+    p = q.precision()
+    B, S, H, D = q.shape()
+    for t in (grad_output, k, v, o):
+        assert t.precision() is p and t.shape() == [B, S, H, D], "shape or precision mismatch"
+    assert o.lse is not None, "o must come from attention()"
+    if S == 0 or B * H == 0:
+        return Tensor.zeros([B, S, H, D], p), Tensor.zeros([B, S, H, D], p), Tensor.zeros([B, S, H, D], p)
+    dq, dk, dv = Tensor.empty([B, S, H, D], p), Tensor.empty([B, S, H, D], p), Tensor.empty([B, S, H, D], p)
+    code = _dtype_code(p)
+    nbytes = raw.bwd_workspace_bytes(code, B, H, S, D)
+    ws = _workspace(nbytes)
+    raw.bwd_bshd(code, B, S, H, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(),
+                 o.lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
+    return dq, dk, dv
 
 
 def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=True):

@@ -65,9 +65,10 @@ static CpuResult cpu_attention(const std::vector<float>& q, const std::vector<fl
   return r;
 }
 
-static double max_abs_diff(const std::vector<float>& a, const std::vector<double>& b) {
+template <class U>
+static double max_abs_diff(const std::vector<float>& a, const std::vector<U>& b) {
   double m = 0;
-  for (size_t i = 0; i < a.size(); ++i) m = std::max(m, std::fabs(a[i] - b[i]));
+  for (size_t i = 0; i < a.size(); ++i) m = std::max(m, std::fabs(static_cast<double>(a[i]) - static_cast<double>(b[i])));
   return m;
 }
 
@@ -172,6 +173,23 @@ int main() {
       EXPECT(max_abs_diff(dq.to_host_f32(), ref.dq) < 2e-2, "bf16 dQ %g", max_abs_diff(dq.to_host_f32(), ref.dq));
       EXPECT(max_abs_diff(dk.to_host_f32(), ref.dk) < 2e-2, "bf16 dK %g", max_abs_diff(dk.to_host_f32(), ref.dk));
       EXPECT(max_abs_diff(dv.to_host_f32(), ref.dv) < 2e-2, "bf16 dV %g", max_abs_diff(dv.to_host_f32(), ref.dv));
+      // the same tensors in [B,S,H,D] through attention() / attention_backward(): no transposes on the device
+      auto to_bshd = [&](const auto& x) {
+        auto y = x;
+        for (size_t b = 0; b < B; ++b) for (size_t h = 0; h < H; ++h) for (size_t s = 0; s < S; ++s) for (size_t d = 0; d < D; ++d)
+          y[((b * S + s) * H + h) * D + d] = x[((b * H + h) * S + s) * D + d];
+        return y;
+      };
+      const std::vector<size_t> shp2 = {B, S, H, D};
+      const Tensor sq = Tensor::from_f32_as_bf16(to_bshd(q), shp2), sk = Tensor::from_f32_as_bf16(to_bshd(k), shp2),
+                   sv = Tensor::from_f32_as_bf16(to_bshd(v), shp2), sgo = Tensor::from_f32_as_bf16(to_bshd(go), shp2);
+      const Tensor so = it::attention(sq, sk, sv, true);
+      auto [sdq, sdk, sdv] = it::attention_backward(sgo, sq, sk, sv, so, true);
+      it::CommandBatch::poll_device_status();
+      EXPECT(max_abs_diff(so.to_host_f32(), to_bshd(o.to_host_f32())) == 0.0, "[B,S,H,D] O equals [B,H,S,D] O");
+      EXPECT(max_abs_diff(sdk.to_host_f32(), to_bshd(dk.to_host_f32())) == 0.0, "[B,S,H,D] dK equals [B,H,S,D] dK");
+      EXPECT(max_abs_diff(sdv.to_host_f32(), to_bshd(dv.to_host_f32())) == 0.0, "[B,S,H,D] dV equals [B,H,S,D] dV");
+      EXPECT(max_abs_diff(sdq.to_host_f32(), to_bshd(ref.dq)) < 2e-2, "[B,S,H,D] dQ");
     }
     // --- the reference's asserts
     {

@@ -376,3 +376,32 @@ def test_host_step_overlapped_chunks_match_device_resident(it_ctx):
     assert np.array_equal(got[0], whole[0][0])
     assert np.abs(got[1] - whole[2][0]).max() <= 2e-2     # dQ: reduction order may differ
     assert np.array_equal(got[2], whole[3][0]) and np.array_equal(got[3], whole[4][0])
+
+
+@pytest.mark.parametrize("shape,bf16", [((2, 3, 256, 64), True), ((1, 2, 300, 128), True), ((2, 4, 32, 16), False),
+                                        ((1, 3, 100, 40), False), ((2, 2, 64, 64), True)])
+def test_bshd_layout_matches_bhsd(it_ctx, shape, bf16):
+    """attention()/attention_backward() on [B,S,H,D] (strided TMA, no transposes) against the [B,H,S,D] path."""
+    import torch
+    from irontensor_b200 import Precision, Tensor, attention, attention_backward
+    B, H, S, D = shape
+    q, k, v, d_o = seeded(81, B, H, S, D, bf16=bf16)
+    want = gu.run_fwd_bwd(it_ctx, q, k, v, d_o, True, bf16)                    # O, LSE, dQ, dK, dV in [B,H,S,D]
+    mk = Tensor.from_f32_as_bf16 if bf16 else Tensor.from_f32_slice
+    tq, tk, tv, tdo = (mk(np.ascontiguousarray(x.transpose(0, 2, 1, 3)).reshape(-1), [B, S, H, D]) for x in (q, k, v, d_o))
+    o = attention(tq, tk, tv, True)
+    dq, dk, dv = attention_backward(tdo, tq, tk, tv, o, True)
+    assert it_ctx.poll_status() == 0
+    back = lambda t: t.to_f32_host().reshape(B, S, H, D).transpose(0, 2, 1, 3)
+    assert np.array_equal(back(o), want[0])
+    assert np.array_equal(o.lse.to_f32_host().reshape(B, H, S), want[1])
+    assert np.array_equal(back(dk), want[3]) and np.array_equal(back(dv), want[4])
+    if bf16 and S >= 128 and D in (64, 128):
+        assert np.abs(back(dq) - want[2]).max() <= 2e-2      # reduction order of the fp32 accumulator
+    else:
+        assert np.array_equal(back(dq), want[2])
+    # non-causal forward against the oracle, in this layout
+    o2 = attention(tq, tk, tv, False)
+    ref = ol.fwd(q, k, v, False)[0]
+    tol = BF16_MAX_ABS if bf16 else F32_TOL
+    assert np.abs(back(o2) - ref).max() <= tol
