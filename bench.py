@@ -293,7 +293,8 @@ def run_ours(args, rank, world, local_rank):
         "frac": ach / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload if world == 1 else None),
         "peak_source": peaks["source"] + " (burst)", "avg_launch_ms": bwd_avg_ms,
         "frac_of_sustained_peak": ach / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
-        "forward_kernel": {"kernel": "fa_fwd_sm100_kernel", "avg_launch_ms": fwd_avg_ms,
+        "forward_kernel": {"kernel": "fa_fwd_pp_sm100_kernel" if (D == 128 and S >= 4096) else "fa_fwd_sm100_kernel",
+                           "avg_launch_ms": fwd_avg_ms,
                            "achieved": flops_fwd(nbh, S, D) / (fwd_avg_ms * 1e-3) / 1e12,
                            "frac": flops_fwd(nbh, S, D) / (fwd_avg_ms * 1e-3) / 1e12 / peaks["bf16"]},
     }

@@ -281,38 +281,51 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const uint32_t do_addr = smem_addr(smem + T::SMEM_DO);
         const uint32_t ds_addr = smem_addr(smem + T::SMEM_DS);
         auto kmajor_off = [](int kk) -> uint32_t { return (kk >> 2) * T::BLOCK_BYTES + (kk & 3) * 32; };
-        auto issue_st = [&](int st) {   // S^T = K * Q^T
+        // A barrier probe takes a few hundred cycles while the tensor core streams operands out of shared
+        // memory, and the queue in front of the tensor core is short, so a probe between two bursts is a
+        // gap in the MMA stream.  Every burst therefore runs `mid` half-way through: a non-blocking probe
+        // of the barrier the NEXT burst depends on, whose answer is read when this burst has been issued.
+        auto none = [] {};
+        auto issue_st = [&](int st, auto mid) {   // S^T = K * Q^T
           const uint64_t da = make_sdesc(k_addr, 16, 1024);
           const uint64_t db = make_sdesc(q_addr + st * T::TILE_BYTES, 16, 1024);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk)
+          for (int kk = 0; kk < D / 16; ++kk) {
+            if (kk == D / 32) mid();
             umma_ss(tmem_base + T::COL_ST, sdesc_advance(da, kmajor_off(kk)), sdesc_advance(db, kmajor_off(kk)),
                     IDESC_SS, kk > 0);
+          }
           umma_commit(st_full);
         };
-        auto issue_dpt = [&]() {   // dP^T = V * dO^T
+        auto issue_dpt = [&](auto mid) {   // dP^T = V * dO^T
           const uint64_t da = make_sdesc(v_addr, 16, 1024);
           const uint64_t db = make_sdesc(do_addr, 16, 1024);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk)
+          for (int kk = 0; kk < D / 16; ++kk) {
+            if (kk == D / 32) mid();
             umma_ss(tmem_base + T::COL_DPT, sdesc_advance(da, kmajor_off(kk)), sdesc_advance(db, kmajor_off(kk)),
                     IDESC_SS, kk > 0);
+          }
           umma_commit(dpt_full);
         };
-        auto issue_dv = [&](bool first) {   // dV += P^T * dO   (A from TMEM, B = dO N-major)
+        auto issue_dv = [&](bool first, auto mid) {   // dV += P^T * dO   (A from TMEM, B = dO N-major)
           const uint64_t db = make_sdesc(do_addr, T::BLOCK_BYTES, 1024);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
+          for (int kk = 0; kk < 8; ++kk) {
+            if (kk == 4) mid();
             umma_ts(tmem_base + T::COL_DV, tmem_base + T::COL_ST + (kk >> 2) * 64 + (kk & 3) * 8,
                     sdesc_advance(db, kk * 2048), IDESC_ND, (!first || kk > 0) ? 1u : 0u);
+          }
         };
-        auto issue_dk = [&](int st, bool first) {   // dK += dS^T * Q   (A = dS^T K-major, B = Q N-major)
+        auto issue_dk = [&](int st, bool first, auto mid) {   // dK += dS^T * Q   (A = dS^T K-major, B = Q N-major)
           const uint64_t da = make_sdesc(ds_addr, 16, 1024);
           const uint64_t db = make_sdesc(q_addr + st * T::TILE_BYTES, T::BLOCK_BYTES, 1024);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
+          for (int kk = 0; kk < 8; ++kk) {
+            if (kk == 4) mid();
             umma_ss(tmem_base + T::COL_DK, sdesc_advance(da, kmajor_off(kk)), sdesc_advance(db, kk * 2048), IDESC_ND,
                     (!first || kk > 0) ? 1u : 0u);
+          }
         };
         auto issue_dq = [&]() {   // dQ = dS * K   (A = dS M-major from the same buffer, B = K N-major)
           const uint64_t da = make_sdesc(ds_addr, T::BLOCK_BYTES, 1024);
@@ -322,42 +335,49 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             umma_ss(tmem_base + T::COL_DQ, sdesc_advance(da, kk * 2048), sdesc_advance(db, kk * 2048), IDESC_DQ,
                     kk > 0);
         };
+        auto need = [&](bool ready, uint64_t* bar, uint32_t parity, int code) {
+          return ready || mbar_wait_parked(bar, parity, abort_flag, prm.status, code);
+        };
         bool ok = mbar_wait_parked(kv_full, 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
         if (ok) ok = mbar_wait_parked(&q_full[0], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
         if (ok) {
           tc_fence_after();
-          issue_st(0);
+          issue_st(0, none);
         }
+        bool r_do = false, r_dq = false, r_p = false, r_q = false, r_ds = false;   // answers of the early probes
         for (int n = 0; n < n_iter && ok; ++n) {
           const int st = n & 1;
-          const uint32_t ph = (n >> 1) & 1;
-          ok = mbar_wait_parked(do_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-          if (!ok) break;
-          if (n > 0) {   // dQ(n-1) must have left TMEM before dP^T(n) overwrites those columns
-            ok = mbar_wait_parked(dq_empty, (n - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
-            if (!ok) break;
-          }
-          tc_fence_after();
-          issue_dpt();
-          ok = mbar_wait_parked(p_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+          const uint32_t par = n & 1;
+          const bool more = (n + 1 < n_iter);
+          const int st_n = (n + 1) & 1;
+          const uint32_t ph_n = ((n + 1) >> 1) & 1;
+          ok = need(r_do, do_full, par, DEV_ERR_TIMEOUT_LOAD);
+          // dQ(n-1) must have left TMEM before dP^T(n) overwrites those columns
+          if (ok && n > 0) ok = need(r_dq, dq_empty, (n - 1) & 1, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
-          issue_dv(n == 0);
+          issue_dpt([&] { r_p = mbar_test_wait(p_full, par); });
+          ok = need(r_p, p_full, par, DEV_ERR_TIMEOUT_SOFTMAX);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dv(n == 0, [&] { r_q = more && mbar_test_wait(&q_full[st_n], ph_n); });
           umma_commit(do_empty);
-          if (n + 1 < n_iter) {
-            const int st_n = (n + 1) & 1;
-            const uint32_t ph_n = ((n + 1) >> 1) & 1;
-            ok = mbar_wait_parked(&q_full[st_n], ph_n, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+          r_ds = false;
+          if (more) {
+            ok = need(r_q, &q_full[st_n], ph_n, DEV_ERR_TIMEOUT_LOAD);
             if (!ok) break;
             tc_fence_after();
-            issue_st(st_n);
+            issue_st(st_n, [&] { r_ds = mbar_test_wait(ds_full, par); });
           }
-          ok = mbar_wait_parked(ds_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+          ok = need(r_ds, ds_full, par, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
           issue_dq();
           umma_commit(dq_full);
-          issue_dk(st, n == 0);
+          issue_dk(st, n == 0, [&] {
+            r_do = more && mbar_test_wait(do_full, par ^ 1);
+            r_dq = more && mbar_test_wait(dq_empty, par);
+          });
           umma_commit(&q_empty[st]);
         }
         if (ok) umma_commit(dkv_done);

@@ -1,4 +1,6 @@
-// Causal / full scaled-dot-product attention forward for bf16 inputs on sm_100a.
+// Causal / full scaled-dot-product attention forward for bf16 inputs on sm_100a: two query tiles per
+// CTA sharing each K/V tile.  The launcher uses it for head_dim 64 and for sequences below 4096 keys
+// (half as many CTA start-ups per unit of work as fa_fwd_pp_sm100.cuh, which takes the long ones).
 //
 // Replaces, for bf16 tensors with head_dim 64 or 128, the reference project's forward kernels
 // (src/shaders/flash_attention.metal:45-163 online softmax; :167-223 exact softmax) and adds the
@@ -27,6 +29,7 @@ template <int D>
 struct FwdTraits {
   static constexpr int BM = 128;            // query rows per tile
   static constexpr int BN = 128;            // keys per tile
+  static constexpr int QT_PER_CTA = 2;      // query tiles per CTA
   static constexpr int STAGES = (D == 128) ? 2 : 4;
   static constexpr int TILE_BYTES = BM * D * 2;          // one Q, K or V tile
   static constexpr int BLOCK_BYTES = 128 * 128;          // one [128 x 64] bf16 swizzled block

@@ -17,7 +17,10 @@
 #include <new>
 
 #include "fa_bwd_sm100.cuh"
+#include <type_traits>
+
 #include "fa_fwd_sm100.cuh"
+#include "fa_fwd_pp_sm100.cuh"
 #include "fa_generic.cuh"
 #include "selftest_sm100.cuh"
 
@@ -162,11 +165,15 @@ void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
   ctx->launches += 3;
 }
 
-template <int D>
+// The two tensor-core forward kernels: one query tile per CTA with the softmax groups alternating over key
+// tiles (long sequences: the tensor core never waits for a softmax), or two query tiles per CTA sharing
+// each K/V tile (short sequences: half as many CTA start-ups per unit of work).
+template <int D, bool PP>
 it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, void* o, float* lse, const it::TensorStrides& stv) {
   const int BH = B * H;
-  using T = it::FwdTraits<D>;
+  using T = std::conditional_t<PP, it::FwdPPTraits<D>, it::FwdTraits<D>>;
+  auto kernel = PP ? it::fa_fwd_pp_sm100_kernel<D> : it::fa_fwd_sm100_kernel<D>;
   CUtensorMap mq, mk, mv;
   it_status st;
   if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
@@ -174,7 +181,7 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   if ((st = make_tmap(ctx, &mv, v, B, H, S, D, stv, 128)) != IT_OK) return st;
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    IT_CUDA(cudaFuncSetAttribute(it::fa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    IT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
   }
   it::FwdParams p;
@@ -186,9 +193,9 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.BH = BH;
   p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
-  const int n_pairs = (S + 255) / 256;
+  const int n_ctas_per_slice = (S + T::BM * T::QT_PER_CTA - 1) / (T::BM * T::QT_PER_CTA);
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
-  it::fa_fwd_sm100_kernel<D><<<static_cast<unsigned>(n_pairs) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  kernel<<<static_cast<unsigned>(n_ctas_per_slice) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[0][1], s));
     ctx->ev_valid[0] = true;
@@ -493,8 +500,14 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
   IT_CUDA(cudaSetDevice(ctx->device));
   const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
   if (use_sm100_path(dtype, S, D)) {
-    return D == 128 ? launch_fwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv)
-                    : launch_fwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv);
+    // Crossover measured on B200 (causal): equal at S = 4096, D = 128; the two-tile kernel wins below and
+    // for D = 64 at every length.
+    const bool pp = (D == 128) && (S >= 4096);
+    if (D == 128)
+      return pp ? launch_fwd_sm100<128, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv)
+                : launch_fwd_sm100<128, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv);
+    return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv)
+              : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv);
   }
   if (dtype == IT_F32)
     launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv);
@@ -690,12 +703,10 @@ it_status it_selftest_umma_rate(it_ctx* ctx, it_stream* stream, int32_t variant,
     return fail(IT_ERR_INVALID_ARG, "variant 0..4, ctas 1..1024, iters 1..100000");
   IT_CUDA(cudaSetDevice(ctx->device));
   const int smem = 6 * 128 * 128 + 64;
-  const char* tr = getenv("IT_RATE_TRACE");
-  long long* trace = tr ? reinterpret_cast<long long*>(strtoull(tr, nullptr, 0)) : nullptr;
 #define IT_RATE_CASE(V)                                                                                      \
   case V:                                                                                                    \
     IT_CUDA(cudaFuncSetAttribute(it::umma_rate_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    it::umma_rate_kernel<V><<<ctas, 128, smem, stream->s>>>(iters, ctx->d_status, trace);                           \
+    it::umma_rate_kernel<V><<<ctas, 128, smem, stream->s>>>(iters, ctx->d_status);                           \
     break;
   switch (variant) {
     IT_RATE_CASE(0)

@@ -149,7 +149,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 // that operand path.  VARIANT 0: A, B K-major smem, N=128.  1: same, N=256.  2: A from TMEM,
 // B N-major smem, N=128.  3: A M-major, B N-major smem, N=128.  4: A from TMEM, B N-major, N=256.
 template <int VARIANT>
-__global__ void __launch_bounds__(128, 1) umma_rate_kernel(int iters, int* status, long long* trace) {
+__global__ void __launch_bounds__(128, 1) umma_rate_kernel(int iters, int* status) {
   using namespace ptx;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int N = (VARIANT == 1 || VARIANT == 4) ? 256 : 128;
@@ -198,55 +198,6 @@ __global__ void __launch_bounds__(128, 1) umma_rate_kernel(int iters, int* statu
     }
     umma_commit(bar);
     mbar_wait(bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA, 4000000000ull);
-    if (trace != nullptr && blockIdx.x == 0) {
-      uint64_t* done_bar = bar + 2;
-      mbar_init(done_bar, 1);
-      fence_mbar_init();
-      mbar_arrive(done_bar);   // phase 0 complete
-      const uint32_t a_addr = smem_addr(sA), b_addr = smem_addr(sB);
-      auto burst = [&]() {
-        for (int kk = 0; kk < 16; ++kk)
-          umma_ss(tmem_base, make_sdesc(a_addr, 16, 1024), make_sdesc(b_addr, 16, 1024), make_idesc(128, 128, false, false), 1);
-      };
-      auto settle = [&]() { for (int i = 0; i < 4; ++i) __nanosleep(1000); };
-      long long t0, t1;
-      // C: idle thread, completed barrier
-      settle();
-      t0 = clock64(); if (mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[0] = t1 - t0; }
-      // B: burst, then wait
-      settle();
-      t0 = clock64(); burst(); t1 = clock64(); trace[1] = t1 - t0;
-      t0 = clock64(); if (mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[2] = t1 - t0; }
-      // A: burst, commit, then wait
-      settle();
-      burst();
-      t0 = clock64(); umma_commit(bar + 1); t1 = clock64(); trace[3] = t1 - t0;
-      t0 = clock64(); if (mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[4] = t1 - t0; }
-      // A3: burst, three commits, then wait, fence, and the time until a further MMA is accepted
-      settle();
-      burst();
-      t0 = clock64(); umma_commit(bar + 1); umma_commit(bar + 1); umma_commit(bar + 1); t1 = clock64(); trace[5] = t1 - t0;
-      t0 = clock64(); if (mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[6] = t1 - t0; }
-      t0 = clock64(); tc_fence_after();
-      umma_ss(tmem_base, make_sdesc(a_addr, 16, 1024), make_sdesc(b_addr, 16, 1024), make_idesc(128, 128, false, false), 1);
-      t1 = clock64(); trace[7] = t1 - t0;
-      // E: alternatives for the wait on a completed barrier
-      settle();
-      t0 = clock64(); if (mbar_test_wait(done_bar, 0)) { t1 = clock64(); trace[9] = t1 - t0; }
-      settle();
-      t0 = clock64(); if (mbar_try_wait(done_bar, 0)) { t1 = clock64(); trace[10] = t1 - t0; }
-      settle();
-      t0 = clock64(); if (mbar_test_wait(done_bar, 0) || mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[11] = t1 - t0; }
-      settle();
-      t0 = clock64(); if (mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[12] = t1 - t0; }
-      t0 = clock64(); if (mbar_wait(done_bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[13] = t1 - t0; }
-      // D: time from commit to the barrier completing when the pipe is empty (commit latency)
-      settle();
-      uint64_t* cb = bar + 1;   // completed 4 times so far: phase parity 0 next
-      t0 = clock64(); umma_commit(cb);
-      if (mbar_wait(cb, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA)) { t1 = clock64(); trace[8] = t1 - t0; }
-      settle();
-    }
   }
   tc_fence_before();
   __syncthreads();

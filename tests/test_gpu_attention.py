@@ -405,3 +405,16 @@ def test_bshd_layout_matches_bhsd(it_ctx, shape, bf16):
     ref = ol.fwd(q, k, v, False)[0]
     tol = BF16_MAX_ABS if bf16 else F32_TOL
     assert np.abs(back(o2) - ref).max() <= tol
+
+
+@pytest.mark.parametrize("S,causal,qk_scale", [(4096, True, 1.0), (4100, True, 1.0), (4225, False, 1.0), (4352, True, 3.0),
+                                               (4480, False, 3.0)])
+def test_bf16_long_sequence_forward(it_ctx, S, causal, qk_scale):
+    """The forward kernel for long sequences (head_dim 128, 4096 keys or more: one query tile per CTA, the two
+    softmax groups alternating over key tiles) against the oracle: ragged lengths, odd and even tile counts, no
+    mask, and scores spread widely enough that the reference maximum is raised (O rescaled) many times."""
+    q, k, v, _ = seeded(90 + S, 1, 2, S, 128, bf16=True, qk_scale=qk_scale)
+    o, lse = gu.run_fwd(it_ctx, q, k, v, causal, bf16=True)
+    ro, rlse = ol.fwd(q, k, v, causal)
+    assert np.abs(lse - rlse).max() <= 1e-4 * max(1.0, qk_scale ** 2)
+    check_bf16(o, ro, f"S={S} causal={causal} O")
