@@ -126,6 +126,24 @@ it_status it_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32
                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
                            size_t workspace_bytes);
 
+/* Grouped-query attention on [batch, seq, heads, head_dim] queries and [batch, seq, kv_heads, head_dim]
+ * keys/values, kv_heads dividing heads; query head h reads K/V head h / (heads / kv_heads).  The reference
+ * expands K and V to `heads` heads with repeat_kv before its attention and sums the expanded gradients
+ * back with repeat_kv_backward after it (src/ops/repeat_kv.rs:68-149, 151-232; kernels
+ * src/shaders/repeat_kv.metal:19-47, 49-88; call sites src/train/forward.rs:117-118,
+ * src/train/backward.rs:121-122).  Here the head mapping is a coordinate of the K/V tensor maps and the
+ * backward accumulates dK/dV over the group's query heads in tensor memory, so neither the expanded
+ * copies nor the expanded gradients exist.  o, d_o, dq: [batch, seq, heads, head_dim]; dk, dv:
+ * [batch, seq, kv_heads, head_dim]; lse: [batch, heads, seq].  Workspace size:
+ * it_flash_attention_bwd_workspace_bytes with the QUERY head count.  kv_heads == heads is it_attention_*. */
+it_status it_attention_gqa_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq,
+                               int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t causal, const void* q,
+                               const void* k, const void* v, void* o, float* lse);
+it_status it_attention_gqa_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq,
+                               int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t causal, const void* q,
+                               const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                               void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes);
+
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)
  *

@@ -57,7 +57,8 @@ struct BwdTraits {
 };
 
 struct BwdParams {
-  ptx::TensorStrides st;   // layout of q, k, v, o, dO and of dq, dk, dv
+  ptx::TensorStrides st;   // layout of q, o, dO and dq
+  ptx::TensorStrides st_kv;  // layout of k, v, dk, dv: heads / group heads (grouped-query attention), group 1 otherwise
   const float* lse2_pad;   // [BH, S_pad] LSE * log2(e), +inf in the padding
   const float* delta_pad;  // [BH, S_pad] rowsum(dO*O), 0 in the padding
   float* dq_accum;         // [BH, S, D] fp32, zeroed by the caller
@@ -176,11 +177,17 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // their Q/dO streams and the fp32 dQ accumulator they add into stay in L2.  Within a slice key
   // tile 0 comes first: under the causal mask it sees every query tile and has the most work.
   const int n_k_tiles = (S + T::BM - 1) / T::BM;
-  const int bh = static_cast<int>(blockIdx.x) / n_k_tiles;
+  // A CTA owns one key tile of one K/V head and loops over the query heads of that head's group
+  // (grouped-query attention: dK and dV are the sums over the group, accumulated in TMEM, so the
+  // reference's repeat_kv_backward pass, src/shaders/repeat_kv.metal:49-88, does not exist here).
+  const int G = prm.st_kv.group;
+  const int kv_heads = prm.st.heads / G;
+  const int bhk = static_cast<int>(blockIdx.x) / n_k_tiles;   // batch * kv_heads + kv_head
   const int kt = static_cast<int>(blockIdx.x) % n_k_tiles;
-  const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
+  const int hkv = bhk % kv_heads, bt = bhk / kv_heads;        // TMA coordinates of the K/V slice
+  const int bh0 = bt * prm.st.heads + hkv * G;                // first query slice of the group
   const int i0 = prm.causal ? kt : 0;
-  const int n_iter = n_q_tiles - i0;
+  const int n_iter = (n_q_tiles - i0) * G;                    // query tiles of every query head of the group
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -240,19 +247,24 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         prefetch_tensormap(&tmap_dq);
         mbar_arrive_expect_tx(kv_full, 2 * T::TILE_BYTES);
         for (int b = 0; b < T::NBLK; ++b) {
-          tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, hd, bt);
-          tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, hd, bt);
+          tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, hkv, bt);
+          tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, hkv, bt);
         }
+        int g = 0, qi = i0 - 1;   // query head within the group, query tile
         for (int n = 0; n < n_iter; ++n) {
           const int st = n & 1;
           const uint32_t ph = (n >> 1) & 1;
-          const int qi = i0 + n;
+          if (++qi == n_q_tiles) {
+            qi = i0;
+            ++g;
+          }
+          const int hd = hkv * G + g;   // query head
           if (!mbar_wait_parked(&q_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(&q_full[st], T::TILE_BYTES + 1024);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_Q + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[st], b * 64,
                         qi * T::BN, hd, bt);
-          const size_t row0 = static_cast<size_t>(bh) * prm.S_pad + static_cast<size_t>(qi) * T::BN;
+          const size_t row0 = static_cast<size_t>(bh0 + g) * prm.S_pad + static_cast<size_t>(qi) * T::BN;
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(
                   smem_addr(smem + T::SMEM_LSE + st * 512)),
@@ -399,9 +411,10 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = true;
       uint32_t ra[16], rb[16];
       uint32_t p_keep[32];   // this thread's 64 P^T values, packed bf16, kept between the two phases
+      int qi = i0 - 1;
       for (int n = 0; n < n_iter; ++n) {
         const int st = n & 1;
-        const int qi = i0 + n;
+        if (++qi == n_q_tiles) qi = i0;
         const bool diag = prm.causal && (qi == kt);
         const float* lse_s = reinterpret_cast<const float*>(smem + T::SMEM_LSE + st * 512) + half * 64;
         const float* dl_s = reinterpret_cast<const float*>(smem + T::SMEM_DELTA + st * 512) + half * 64;
@@ -491,7 +504,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // each math group writes one half of the head dimension of its key row's dV and dK
         tc_fence_after();
         constexpr int HC = D / 2;
-        const long long out_off = prm.st.slice(bh) + static_cast<long long>(k_row) * prm.st.row + half * HC;
+        const long long out_off = prm.st_kv.slice(bh0) + static_cast<long long>(k_row) * prm.st_kv.row + half * HC;
         __nv_bfloat16* dv_row = prm.dv + out_off;
         __nv_bfloat16* dk_row = prm.dk + out_off;
 #pragma unroll 1
@@ -533,7 +546,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = true;
       uint32_t r[D / 32][32];
       int g = 0;   // chunks handled so far
+      int qi = i0 - 1, bh_q = bh0;   // query tile and query slice of the tile being drained
       for (int n = 0; n < n_iter && ok; ++n) {
+        if (++qi == n_q_tiles) {
+          qi = i0;
+          ++bh_q;
+        }
         ok = mbar_wait_parked(dq_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -561,7 +579,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           mbar_arrive(&dqs_full[buf]);
           if (issuer) {
             if (mbar_wait_parked(&dqs_full[buf], use & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX)) {
-              tma_reduce_add_3d(&tmap_dq, stage, c * 32, (i0 + n) * T::BN, bh);
+              tma_reduce_add_3d(&tmap_dq, stage, c * 32, qi * T::BN, bh_q);
               bulk_commit_group();
               if (g >= 1) {   // the previous chunk's reduce has read the other buffer: hand it back
                 bulk_wait_group_read<1>();

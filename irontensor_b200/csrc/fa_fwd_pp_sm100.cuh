@@ -98,6 +98,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int bh = static_cast<int>(blockIdx.x) / n_qt;
   const int qt = n_qt - 1 - static_cast<int>(blockIdx.x) % n_qt;
   const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
+  const int hkv = hd / prm.kv_group;                          // the K/V head this query head reads
   const int nkv = prm.causal ? min(qt + 1, n_kv_total) : n_kv_total;
 
   if (threadIdx.x == 0) {
@@ -158,7 +159,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
-                        i * T::BN, hd, bt);
+                        i * T::BN, hkv, bt);
         }
       }
     } else if (warp == 3) {
@@ -173,7 +174,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
-                        i * T::BN, hd, bt);
+                        i * T::BN, hkv, bt);
         }
       }
     } else if (warp == 1) {

@@ -54,6 +54,7 @@ struct FwdParams {
   int BH;
   int causal;
   float scale_log2;     // 1/sqrt(D) * log2(e)
+  int kv_group;         // query heads per K/V head (grouped-query attention; 1 otherwise)
 };
 
 template <int D>
@@ -86,6 +87,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int bh = static_cast<int>(blockIdx.x) / n_pairs;
   const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) % n_pairs;
   const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
+  const int hkv = hd / prm.kv_group;                          // the K/V head this query head reads
   int n_kv[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -154,12 +156,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
-                        j * T::BN, hd, bt);
+                        j * T::BN, hkv, bt);
           if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
           mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
-                        j * T::BN, hd, bt);
+                        j * T::BN, hkv, bt);
         }
       }
     } else if (warp == 1) {

@@ -46,7 +46,7 @@ template <typename ST, int DP>
 __global__ void __launch_bounds__(256)
 fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
                       ST* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
-                      TensorStrides st) {
+                      TensorStrides st, TensorStrides skv) {
   constexpr int BM = 64;
   constexpr int BN = (DP >= 128) ? 32 : 64;
   constexpr int NCH = DP / 16;              // float4 chunks per thread
@@ -63,6 +63,8 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   const bool row_ok = row < S;
   const size_t base = static_cast<size_t>(st.slice(bh));
   const size_t RS = static_cast<size_t>(st.row);
+  const size_t kbase = static_cast<size_t>(skv.slice(bh));   // the K/V head this query head reads
+  const size_t KRS = static_cast<size_t>(skv.row);
 
   float4 qv[NCH], acc[NCH];
 #pragma unroll
@@ -85,7 +87,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
     for (int i = tid; i < BN * DP; i += 256) {
       const int kk = i / DP, d = i % DP;
       const bool okk = (kk < nk) && (d < D);
-      const size_t g = base + static_cast<size_t>(k0 + kk) * RS + d;
+      const size_t g = kbase + static_cast<size_t>(k0 + kk) * KRS + d;
       sK[i] = okk ? ld_as_f32(k + g) : 0.f;
       sV[i] = okk ? ld_as_f32(v + g) : 0.f;
     }
@@ -167,7 +169,7 @@ template <int NJ>
 __global__ void __launch_bounds__(128)
 fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                        float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
-                       TensorStrides st) {
+                       TensorStrides st, TensorStrides skv) {
   constexpr int RB = 16, RW = 4, TK = 32;
   extern __shared__ __align__(16) float sm[];
   const int DS = D + 4;                       // padded row stride (floats)
@@ -183,6 +185,8 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
   const int r0 = rb * RB;
   const size_t base = static_cast<size_t>(st.slice(bh));
   const size_t RS = static_cast<size_t>(st.row);
+  const size_t kbase = static_cast<size_t>(skv.slice(bh));   // the K/V head this query head reads
+  const size_t KRS = static_cast<size_t>(skv.row);
   const int k_end_cta = causal ? min(S, r0 + RB) : S;
   const int n_tiles = (k_end_cta + TK - 1) / TK;
 
@@ -195,7 +199,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
       float* pk = dk + key * DS + 4 * c;
       float* pv = dv + key * DS + 4 * c;
       if (k0 + key < k_end_cta) {
-        const size_t g = base + static_cast<size_t>(k0 + key) * RS + 4 * c;
+        const size_t g = kbase + static_cast<size_t>(k0 + key) * KRS + 4 * c;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(pk))), "l"(k + g));
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(pv))), "l"(v + g));
       } else {   // rows past the end: zeros, so that 0 * V stays 0
@@ -329,33 +333,40 @@ __global__ void fa_bwd_generic_delta_kernel(const ST* __restrict__ o, const ST* 
   if (lane == 0) delta[row] = a;
 }
 
-// MODE 0: one warp per query row -> dQ.   MODE 1: one warp per key row -> dK, dV.
-// Lanes split the head dimension (lane, lane+32, ...); the two dot products per (query, key)
-// pair are completed with a butterfly over the warp.
+// MODE 0: one warp per query row -> dQ.   MODE 1: one warp per key row of a K/V head -> dK, dV, summed
+// over the query heads of its group (the reference's repeat_kv_backward, src/shaders/repeat_kv.metal:49-88,
+// folded in).  Lanes split the head dimension (lane, lane+32, ...); the two dot products per
+// (query, key) pair are completed with a butterfly over the warp.  blockIdx.y is the query slice
+// (MODE 0) or the K/V slice batch * kv_heads + kv_head (MODE 1).
 template <typename ST, int MODE>
 __global__ void __launch_bounds__(128)
 fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
                       const ST* __restrict__ d_o, const float* __restrict__ lse, const float* __restrict__ delta,
                       ST* __restrict__ dq, ST* __restrict__ dk, ST* __restrict__ dv, int S, int D, int causal,
-                      float scale, TensorStrides st) {
+                      float scale, TensorStrides st, TensorStrides skv) {
   const int lane = threadIdx.x & 31;
   const int r = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5);
-  const int bh = blockIdx.y;
   if (r >= S) return;
-  const size_t base = static_cast<size_t>(st.slice(bh));
+  const int G = (MODE == 0) ? 1 : skv.group;
+  const int kv_heads = skv.heads / skv.group;
+  // first query slice this warp works on: its own (MODE 0), or the first of the K/V head's group (MODE 1)
+  const int bh0 = (MODE == 0) ? static_cast<int>(blockIdx.y)
+                              : (static_cast<int>(blockIdx.y) / kv_heads) * skv.heads +
+                                    (static_cast<int>(blockIdx.y) % kv_heads) * skv.group;
+  const size_t kbase = static_cast<size_t>(skv.slice(bh0));
+  const size_t KRS = static_cast<size_t>(skv.row);
   const size_t RS = static_cast<size_t>(st.row);
-  const float* lse_h = lse + static_cast<size_t>(bh) * S;
-  const float* dl_h = delta + static_cast<size_t>(bh) * S;
   float a0[4], a1[4], g0[4], g1[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int d = lane + 32 * j;
     const bool in = d < D;
-    const size_t off = base + static_cast<size_t>(r) * RS + d;
     if (MODE == 0) {
+      const size_t off = static_cast<size_t>(st.slice(bh0)) + static_cast<size_t>(r) * RS + d;
       a0[j] = in ? ld_as_f32(q + off) : 0.f;     // q_i
       a1[j] = in ? ld_as_f32(d_o + off) : 0.f;   // dO_i
     } else {
+      const size_t off = kbase + static_cast<size_t>(r) * KRS + d;
       a0[j] = in ? ld_as_f32(k + off) : 0.f;     // k_j
       a1[j] = in ? ld_as_f32(v + off) : 0.f;     // v_j
     }
@@ -364,44 +375,45 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   }
   const int lo = (MODE == 0) ? 0 : (causal ? r : 0);
   const int hi = (MODE == 0) ? (causal ? r + 1 : S) : S;
-  const float lse_r = (MODE == 0) ? lse_h[r] : 0.f;
-  const float dl_r = (MODE == 0) ? dl_h[r] : 0.f;
-  for (int x = lo; x < hi; ++x) {
-    float b0[4], b1[4];
-    float s = 0.f, dp = 0.f;
+  for (int g = 0; g < G; ++g) {
+    const int bh = bh0 + g;
+    const size_t base = static_cast<size_t>(st.slice(bh));
+    const float* lse_h = lse + static_cast<size_t>(bh) * S;
+    const float* dl_h = delta + static_cast<size_t>(bh) * S;
+    const float lse_r = (MODE == 0) ? lse_h[r] : 0.f;
+    const float dl_r = (MODE == 0) ? dl_h[r] : 0.f;
+    for (int x = lo; x < hi; ++x) {
+      float b0[4], b1[4];
+      float s = 0.f, dp = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int d = lane + 32 * j;
-      const bool in = d < D;
-      const size_t off = base + static_cast<size_t>(x) * RS + d;
-      if (MODE == 0) {
-        b0[j] = in ? ld_as_f32(k + off) : 0.f;   // k_x
-        b1[j] = in ? ld_as_f32(v + off) : 0.f;   // v_x
-        s = fmaf(a0[j], b0[j], s);
-        dp = fmaf(a1[j], b1[j], dp);
-      } else {
-        b0[j] = in ? ld_as_f32(q + off) : 0.f;   // q_x
-        b1[j] = in ? ld_as_f32(d_o + off) : 0.f; // dO_x
+      for (int j = 0; j < 4; ++j) {
+        const int d = lane + 32 * j;
+        const bool in = d < D;
+        if (MODE == 0) {
+          const size_t off = kbase + static_cast<size_t>(x) * KRS + d;
+          b0[j] = in ? ld_as_f32(k + off) : 0.f;   // k_x
+          b1[j] = in ? ld_as_f32(v + off) : 0.f;   // v_x
+        } else {
+          const size_t off = base + static_cast<size_t>(x) * RS + d;
+          b0[j] = in ? ld_as_f32(q + off) : 0.f;   // q_x
+          b1[j] = in ? ld_as_f32(d_o + off) : 0.f; // dO_x
+        }
         s = fmaf(a0[j], b0[j], s);
         dp = fmaf(a1[j], b1[j], dp);
       }
-    }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      s += __shfl_xor_sync(0xffffffffu, s, off);
-      dp += __shfl_xor_sync(0xffffffffu, dp, off);
-    }
-    const float lse_x = (MODE == 0) ? lse_r : lse_h[x];
-    const float dl_x = (MODE == 0) ? dl_r : dl_h[x];
-    const float p = g_ex2(fmaf(s, scale * 1.4426950408889634f, -lse_x * 1.4426950408889634f));
-    const float ds = p * (dp - dl_x);
+      for (int off = 16; off > 0; off >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, off);
+        dp += __shfl_xor_sync(0xffffffffu, dp, off);
+      }
+      const float lse_x = (MODE == 0) ? lse_r : lse_h[x];
+      const float dl_x = (MODE == 0) ? dl_r : dl_h[x];
+      const float p = g_ex2(fmaf(s, scale * 1.4426950408889634f, -lse_x * 1.4426950408889634f));
+      const float ds = p * (dp - dl_x);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (MODE == 0) {
-        g0[j] = fmaf(ds, b0[j], g0[j]);          // dq += ds * k_x
-      } else {
-        g0[j] = fmaf(ds, b0[j], g0[j]);          // dk += ds * q_x
-        g1[j] = fmaf(p, b1[j], g1[j]);           // dv += p * dO_x
+      for (int j = 0; j < 4; ++j) {
+        g0[j] = fmaf(ds, b0[j], g0[j]);            // dq += ds * k_x   or   dk += ds * q_x
+        if (MODE == 1) g1[j] = fmaf(p, b1[j], g1[j]);   // dv += p * dO_x
       }
     }
   }
@@ -409,10 +421,10 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   for (int j = 0; j < 4; ++j) {
     const int d = lane + 32 * j;
     if (d < D) {
-      const size_t off = base + static_cast<size_t>(r) * RS + d;
       if (MODE == 0) {
-        st_from_f32(dq + off, g0[j] * scale);
+        st_from_f32(dq + static_cast<size_t>(st.slice(bh0)) + static_cast<size_t>(r) * RS + d, g0[j] * scale);
       } else {
+        const size_t off = kbase + static_cast<size_t>(r) * KRS + d;
         st_from_f32(dk + off, g0[j] * scale);
         st_from_f32(dv + off, g1[j]);
       }

@@ -90,6 +90,13 @@ it_status make_tmap(it_ctx* ctx, CUtensorMap* map, const void* base, int64_t B, 
 // [B,H,S,D] (flash_attention) and [B,S,H,D] (attention) as strides in elements.
 it::TensorStrides strides_bhsd(int64_t H, int64_t S, int64_t D) { return it::TensorStrides{D, S * D, H * S * D, static_cast<int>(H)}; }
 it::TensorStrides strides_bshd(int64_t H, int64_t S, int64_t D) { return it::TensorStrides{H * D, D, S * H * D, static_cast<int>(H)}; }
+// A K/V tensor with Hkv = H / group heads, indexed by the query slice (see TensorStrides).
+it::TensorStrides strides_kv(bool bshd, int64_t H, int64_t Hkv, int64_t S, int64_t D) {
+  it::TensorStrides t = bshd ? strides_bshd(Hkv, S, D) : strides_bhsd(Hkv, S, D);
+  t.heads = static_cast<int>(H);
+  t.group = static_cast<int>(H / Hkv);
+  return t;
+}
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -112,7 +119,7 @@ int round_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128; }
 
 template <typename ST>
 void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
-                        const void* v, void* o, float* lse, const it::TensorStrides& st) {
+                        const void* v, void* o, float* lse, const it::TensorStrides& st, const it::TensorStrides& skv) {
   const float scale = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;   // exp2 domain
   const dim3 grid((S + 63) / 64, BH);
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
@@ -124,9 +131,9 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
                 *vf = reinterpret_cast<const float*>(v);
     float* of = reinterpret_cast<float*>(o);
     if (D <= 32) {
-      it::fa_fwd_rows_f32_kernel<1><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st);
+      it::fa_fwd_rows_f32_kernel<1><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
     } else if (D <= 64) {
-      it::fa_fwd_rows_f32_kernel<2><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st);
+      it::fa_fwd_rows_f32_kernel<2><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
     } else {
       static bool attr_set[16] = {};
       if (!attr_set[ctx->device & 15]) {
@@ -134,16 +141,16 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
                              (16 * 128 + 4 * 32 * 132 + 512) * 4);
         attr_set[ctx->device & 15] = true;
       }
-      it::fa_fwd_rows_f32_kernel<4><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st);
+      it::fa_fwd_rows_f32_kernel<4><<<g16, 128, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
     }
     ctx->launches += 1;
     return;
   }
   switch (round_dp(D)) {
-    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
-    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
-    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
-    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st); break;
+    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
+    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
+    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
+    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
   }
   ctx->launches += 1;
 }
@@ -151,17 +158,17 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
 template <typename ST>
 void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
                         const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-                        float* delta, const it::TensorStrides& st) {
+                        float* delta, const it::TensorStrides& st, const it::TensorStrides& skv) {
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
   const ST *oo = static_cast<const ST*>(o), *dd = static_cast<const ST*>(d_o);
   const long long rows = static_cast<long long>(BH) * S;
   it::fa_bwd_generic_delta_kernel<ST><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(oo, dd, delta, rows, S, D, st);
-  const dim3 grid((S + 3) / 4, BH);
-  it::fa_bwd_generic_kernel<ST, 0><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq),
-                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale, st);
-  it::fa_bwd_generic_kernel<ST, 1><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq),
-                                                        static_cast<ST*>(dk), static_cast<ST*>(dv), S, D, causal, scale, st);
+  const dim3 grid((S + 3) / 4, BH), grid_kv((S + 3) / 4, BH / skv.group);
+  it::fa_bwd_generic_kernel<ST, 0><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq), static_cast<ST*>(dk),
+                                                        static_cast<ST*>(dv), S, D, causal, scale, st, skv);
+  it::fa_bwd_generic_kernel<ST, 1><<<grid_kv, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq), static_cast<ST*>(dk),
+                                                           static_cast<ST*>(dv), S, D, causal, scale, st, skv);
   ctx->launches += 3;
 }
 
@@ -170,15 +177,17 @@ void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
 // each K/V tile (short sequences: half as many CTA start-ups per unit of work).
 template <int D, bool PP>
 it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
-                           const void* v, void* o, float* lse, const it::TensorStrides& stv) {
+                           const void* v, void* o, float* lse, const it::TensorStrides& stv,
+                           const it::TensorStrides& skv) {
   const int BH = B * H;
+  const int Hkv = H / skv.group;
   using T = std::conditional_t<PP, it::FwdPPTraits<D>, it::FwdTraits<D>>;
   auto kernel = PP ? it::fa_fwd_pp_sm100_kernel<D> : it::fa_fwd_sm100_kernel<D>;
   CUtensorMap mq, mk, mv;
   it_status st;
   if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mk, k, B, H, S, D, stv, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mv, v, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, k, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, v, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
@@ -193,6 +202,7 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.BH = BH;
   p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
+  p.kv_group = skv.group;
   const int n_ctas_per_slice = (S + T::BM * T::QT_PER_CTA - 1) / (T::BM * T::QT_PER_CTA);
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
   kernel<<<static_cast<unsigned>(n_ctas_per_slice) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
@@ -230,14 +240,16 @@ BwdWorkspace bwd_workspace_layout(it_dtype dtype, int64_t BH, int64_t S, int64_t
 template <int D>
 it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk,
-                           void* dv, uint8_t* ws, const BwdWorkspace& w, const it::TensorStrides& stv) {
+                           void* dv, uint8_t* ws, const BwdWorkspace& w, const it::TensorStrides& stv,
+                           const it::TensorStrides& skv) {
   const int BH = B * H;
+  const int Hkv = H / skv.group;
   using T = it::BwdTraits<D>;
   CUtensorMap mq, mk, mv, mdo;
   it_status st;
   if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mk, k, B, H, S, D, stv, 128)) != IT_OK) return st;
-  if ((st = make_tmap(ctx, &mv, v, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, k, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, v, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mdo, d_o, B, H, S, D, stv, 128)) != IT_OK) return st;
   // fp32 dQ accumulator [BH, S, D]: boxes of 32 columns x 128 rows for the TMA reduce-add
   CUtensorMap mdq;
@@ -266,6 +278,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
       w.S_pad, BH, stv);
   it::BwdParams p;
   p.st = stv;
+  p.st_kv = skv;
   p.lse2_pad = lse2;
   p.delta_pad = delta;
   p.dq_accum = dq_accum;
@@ -280,7 +293,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const int n_kt = (S + 127) / 128;
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
-  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p);
+  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p);
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
@@ -487,11 +500,18 @@ it_status it_buf_memset_async(it_ctx* ctx, it_stream* stream, void* dev, int val
   return IT_OK;
 }
 
-static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
-                                    int32_t D, int32_t causal, const void* q, const void* k, const void* v, void* o,
-                                    float* lse, bool bshd) {
+static it_status check_kv_heads(int32_t H, int32_t Hkv) {
+  if (Hkv < 1 || Hkv > H || H % Hkv != 0)
+    return fail(IT_ERR_INVALID_ARG, "kv_heads must divide heads: heads %d, kv_heads %d", H, Hkv);
+  return IT_OK;
+}
+
+static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t Hkv,
+                                    int32_t S, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
+                                    void* o, float* lse, bool bshd) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
+  if (H > 0 && (st = check_kv_heads(H, Hkv)) != IT_OK) return st;
   const int BH = B * H;
   if (S == 0 || BH == 0) return IT_OK;   // src/ops/flash_attention.rs:102-104, src/ops/attention.rs:313-315
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
@@ -499,20 +519,21 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
     return fail(IT_ERR_ALIGNMENT, "q, k, v and o must be 16-byte aligned");
   IT_CUDA(cudaSetDevice(ctx->device));
   const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
+  const it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
   if (use_sm100_path(dtype, S, D)) {
     // Crossover measured on B200 (causal): equal at S = 4096, D = 128; the two-tile kernel wins below and
     // for D = 64 at every length.
     const bool pp = (D == 128) && (S >= 4096);
     if (D == 128)
-      return pp ? launch_fwd_sm100<128, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv)
-                : launch_fwd_sm100<128, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv);
-    return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv)
-              : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv);
+      return pp ? launch_fwd_sm100<128, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv)
+                : launch_fwd_sm100<128, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv);
+    return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv)
+              : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv);
   }
   if (dtype == IT_F32)
-    launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv);
+    launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
   else
-    launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv);
+    launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
   IT_CUDA(cudaGetLastError());
   return IT_OK;
 }
@@ -520,12 +541,18 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
 it_status it_flash_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
                                  int32_t D, int32_t causal, const void* q, const void* k, const void* v, void* o,
                                  float* lse) {
-  return attention_fwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, lse, false);
+  return attention_fwd_impl(ctx, stream, dtype, B, H, H, S, D, causal, q, k, v, o, lse, false);
 }
 
 it_status it_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H, int32_t D,
                            int32_t causal, const void* q, const void* k, const void* v, void* o, float* lse) {
-  return attention_fwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, lse, true);
+  return attention_fwd_impl(ctx, stream, dtype, B, H, H, S, D, causal, q, k, v, o, lse, true);
+}
+
+it_status it_attention_gqa_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H,
+                               int32_t Hkv, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
+                               void* o, float* lse) {
+  return attention_fwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, q, k, v, o, lse, true);
 }
 
 it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int32_t H, int32_t S, int32_t D,
@@ -538,12 +565,13 @@ it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int3
   return IT_OK;
 }
 
-static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
-                                    int32_t D, int32_t causal, const void* q, const void* k, const void* v,
+static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t Hkv,
+                                    int32_t S, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
                                     const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
                                     void* workspace, size_t workspace_bytes, bool bshd) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
+  if (H > 0 && (st = check_kv_heads(H, Hkv)) != IT_OK) return st;
   const int BH = B * H;
   if (S == 0 || BH == 0) return IT_OK;
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || d_o == nullptr || lse == nullptr ||
@@ -560,16 +588,17 @@ static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
   IT_CUDA(cudaSetDevice(ctx->device));
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
+  const it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
   if (use_sm100_path(dtype, S, D)) {
     return D == 128
-               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv)
-               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv);
+               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv)
+               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv);
   }
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   if (dtype == IT_F32)
-    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv);
+    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv);
   else
-    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv);
+    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv);
   IT_CUDA(cudaGetLastError());
   return IT_OK;
 }
@@ -578,14 +607,22 @@ it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype,
                                  int32_t D, int32_t causal, const void* q, const void* k, const void* v, const void* o,
                                  const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
                                  size_t workspace_bytes) {
-  return attention_bwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
+  return attention_bwd_impl(ctx, stream, dtype, B, H, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
                             workspace_bytes, false);
 }
 
 it_status it_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H, int32_t D,
                            int32_t causal, const void* q, const void* k, const void* v, const void* o, const void* d_o,
                            const float* lse, void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes) {
-  return attention_bwd_impl(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
+  return attention_bwd_impl(ctx, stream, dtype, B, H, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
+                            workspace_bytes, true);
+}
+
+it_status it_attention_gqa_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H,
+                               int32_t Hkv, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
+                               const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                               void* workspace, size_t workspace_bytes) {
+  return attention_bwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
                             workspace_bytes, true);
 }
 

@@ -297,6 +297,17 @@ class raw:
                                           dq, dk, dv, ws, ws_bytes))
 
     @staticmethod
+    def fwd_gqa(dtype, B, S, H, Hkv, D, causal, q, k, v, o, lse, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_gqa_fwd(c.handle, c.stream(), dtype, B, S, H, Hkv, D, int(causal), q, k, v, o, lse))
+
+    @staticmethod
+    def bwd_gqa(dtype, B, S, H, Hkv, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, ws, ws_bytes, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_gqa_bwd(c.handle, c.stream(), dtype, B, S, H, Hkv, D, int(causal), q, k, v, o, d_o,
+                                              lse, dq, dk, dv, ws, ws_bytes))
+
+    @staticmethod
     def bwd_workspace_bytes(dtype, B, H, S, D):
         n = ctypes.c_size_t()
         _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))
@@ -399,6 +410,49 @@ def attention_backward(grad_output, q, k, v, o, causal=True):
     ws = _workspace(nbytes)
     raw.bwd_bshd(code, B, S, H, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(),
                  o.lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
+    return dq, dk, dv
+
+
+def attention_gqa(q, k, v, causal=True):
+    """Grouped-query attention: q [batch, seq, heads, head_dim], k and v [batch, seq, kv_heads, head_dim] with
+    kv_heads dividing heads.  Equal to attention(q, repeat_kv(k), repeat_kv(v), causal) of the reference
+    (src/train/forward.rs:117-139; repeat_kv_gpu, src/ops/repeat_kv.rs:68-149) without the expanded copies:
+    query head h reads K/V head h // (heads // kv_heads).  The result carries `.lse` for attention_gqa_backward."""
+    p = q.precision()
+    assert k.precision() is p and v.precision() is p
+    assert len(q.shape()) == 4 and len(k.shape()) == 4 and len(v.shape()) == 4, "Q, K and V must be 4D"
+    B, S, H, D = q.shape()
+    assert k.shape() == v.shape(), "K and V must have the same shape"
+    Hkv = k.shape()[2]
+    assert k.shape() == [B, S, Hkv, D], "K/V must be [batch, seq, kv_heads, head_dim]"
+    assert Hkv >= 1 and H % Hkv == 0, "num_heads must be divisible by num_kv_heads"   # src/ops/repeat_kv.rs:77-80
+    out = Tensor.empty([B, S, H, D], p)
+    out.lse = Tensor.empty([B, H, S], Precision.FP32)
+    if B * S * H == 0:
+        return out
+    raw.fwd_gqa(_dtype_code(p), B, S, H, Hkv, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                out.lse.data_ptr())
+    return out
+
+
+def attention_gqa_backward(grad_output, q, k, v, o, causal=True):
+    """(dQ, dK, dV) for attention_gqa(): dQ like q, dK and dV like k and v, i.e. already summed over the query
+    heads of each group (the reference's repeat_kv_backward after its attention backward,
+    src/train/backward.rs:102-122; src/ops/repeat_kv.rs:151-232)."""
+    p = q.precision()
+    B, S, H, D = q.shape()
+    Hkv = k.shape()[2]
+    assert grad_output.shape() == [B, S, H, D] and o.shape() == [B, S, H, D]
+    assert k.shape() == [B, S, Hkv, D] and v.shape() == [B, S, Hkv, D] and H % Hkv == 0
+    assert o.lse is not None, "o must come from attention_gqa()"
+    dq, dk, dv = Tensor.empty([B, S, H, D], p), Tensor.empty([B, S, Hkv, D], p), Tensor.empty([B, S, Hkv, D], p)
+    if B * S * H == 0:
+        return dq, dk, dv
+    code = _dtype_code(p)
+    nbytes = raw.bwd_workspace_bytes(code, B, H, S, D)
+    ws = _workspace(nbytes)
+    raw.bwd_gqa(code, B, S, H, Hkv, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                grad_output.data_ptr(), o.lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
     return dq, dk, dv
 
 

@@ -418,3 +418,38 @@ def test_bf16_long_sequence_forward(it_ctx, S, causal, qk_scale):
     ro, rlse = ol.fwd(q, k, v, causal)
     assert np.abs(lse - rlse).max() <= 1e-4 * max(1.0, qk_scale ** 2)
     check_bf16(o, ro, f"S={S} causal={causal} O")
+
+
+@pytest.mark.parametrize("shape,bf16,causal", [
+    ((2, 40, 4, 2, 16), False, True), ((1, 100, 6, 2, 40), False, True), ((1, 300, 8, 1, 64), False, False),
+    ((1, 256, 4, 2, 64), True, True), ((2, 384, 8, 2, 128), True, True), ((1, 300, 4, 1, 128), True, False),
+    ((1, 100, 4, 2, 64), True, True), ((1, 4224, 4, 2, 128), True, True),
+])
+def test_grouped_query_attention(it_ctx, shape, bf16, causal):
+    """attention_gqa / attention_gqa_backward (K/V with fewer heads, no expanded copies, dK/dV summed over the
+    group inside the kernels) against the reference's composition repeat_kv -> attention -> repeat_kv_backward."""
+    from irontensor_b200 import Tensor, attention_gqa, attention_gqa_backward
+    B, S, H, Hkv, D = shape
+    q4, _, _, do4 = seeded(120, B, H, S, D, bf16=bf16)
+    _, k4, v4, _ = seeded(121, B, Hkv, S, D, bf16=bf16)
+    to_bshd = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1, 3))
+    q, k, v, d_o = (to_bshd(x) for x in (q4, k4, v4, do4))
+    mk = Tensor.from_f32_as_bf16 if bf16 else Tensor.from_f32_slice
+    tq, tk, tv, tdo = mk(q.reshape(-1), [B, S, H, D]), mk(k.reshape(-1), [B, S, Hkv, D]), mk(v.reshape(-1), [B, S, Hkv, D]), \
+        mk(d_o.reshape(-1), [B, S, H, D])
+    o = attention_gqa(tq, tk, tv, causal)
+    dq, dk, dv = attention_gqa_backward(tdo, tq, tk, tv, o, causal)
+    assert it_ctx.poll_status() == 0
+    ro, rlse = ol.gqa_fwd(q, k, v, causal)
+    rdq, rdk, rdv = ol.gqa_bwd(q, k, v, d_o, causal)
+    assert np.abs(o.lse.to_f32_host() - rlse).max() <= 1e-4
+    for got, want, name in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        g = got.to_f32_host()
+        assert g.shape == want.shape
+        if bf16:
+            # dK and dV are sums over the group's H // Hkv query heads: their magnitude, and with it the size of a
+            # bf16 rounding step, grows like the square root of the group size
+            scale = math.sqrt(H // Hkv) if name in ("dK", "dV") else 1.0
+            check_bf16(g / scale, want / scale, f"{shape} {name}")
+        else:
+            assert np.abs(g - want).max() <= F32_TOL, f"{shape} {name}: {np.abs(g - want).max()}"
