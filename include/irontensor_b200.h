@@ -144,6 +144,27 @@ it_status it_attention_gqa_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, i
                                const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                                void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes);
 
+/* Rotary position embedding of Q [batch, seq, heads, head_dim] and K [batch, seq, kv_heads, head_dim] in ONE
+ * launch (the reference runs rope() once per tensor: src/ops/rope.rs:22-75, kernel src/shaders/rope.metal:22-61;
+ * call sites src/train/forward.rs:111-112).  theta_i = 1 / base^(2i / head_dim), angle = (position +
+ * position_offset) * theta_i; pairs (2i, 2i+1) are rotated.  inverse != 0 applies the backward rotation
+ * (rope_backward, src/shaders/backward/rope.metal:25-62).  head_dim must be even.  kv_heads may be 0 (K is
+ * then not touched).  In place (q_out == q_in) is allowed.  F32 as in the reference, or BF16. */
+it_status it_rope_qk(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq, int32_t heads,
+                     int32_t kv_heads, int32_t head_dim, float rope_base, int32_t position_offset, int32_t inverse,
+                     const void* q_in, const void* k_in, void* q_out, void* k_out);
+
+/* it_attention_gqa_bwd with the backward of the rotary embedding folded in: q and k are the ROTATED tensors
+ * the forward attended over, dq and dk come back as gradients of the un-rotated ones.  The reference runs
+ * rope_backward as two more passes after its attention backward (src/train/backward.rs:129,132); here the
+ * rotation is applied where dQ and dK leave the chip (the fp32 -> bf16 pass of dQ, the dK epilogue), so
+ * those passes and their 4 x tensor bytes of traffic do not exist.  dv is not affected. */
+it_status it_attention_gqa_bwd_rope(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq,
+                                    int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t causal,
+                                    float rope_base, int32_t position_offset, const void* q, const void* k,
+                                    const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+                                    void* dk, void* dv, void* workspace, size_t workspace_bytes);
+
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)
  *

@@ -28,6 +28,7 @@
 // [64,96): each math group overwrites only columns it has already read), dP^T and dQ (aliased) [128,256),
 // dV [256,256+D), dK [384,384+D).
 #pragma once
+#include "rope.cuh"
 #include "sm100_ptx.cuh"
 
 namespace it {
@@ -125,19 +126,30 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
 }
 
 // ------------------------------------------------------------------ (3) finish
+// With freqs.enabled the gradient is rotated back through the rotary embedding on its way out
+// (src/shaders/backward/rope.metal:25-62), so dq is the gradient of the un-rotated queries.
 __global__ void fa_bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq,
-                                     size_t n_vec4, float scale, int S, int D, ptx::TensorStrides st) {
+                                     size_t n_vec4, float scale, int S, int D, ptx::TensorStrides st,
+                                     const __grid_constant__ RopeFreqs freqs) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_vec4) return;
-  const float4 v = reinterpret_cast<const float4*>(dq_accum)[i];
-  uint2 w;
-  w.x = ptx::pack_bf16(v.x * scale, v.y * scale);
-  w.y = ptx::pack_bf16(v.z * scale, v.w * scale);
+  float4 v = reinterpret_cast<const float4*>(dq_accum)[i];
   const size_t e = i * 4;                       // element index in the [BH, S, D] accumulator
   const size_t row = e / D;
   const int d = static_cast<int>(e - row * D);
   const int bh = static_cast<int>(row / S);
   const int s_ = static_cast<int>(row - static_cast<size_t>(bh) * S);
+  if (freqs.enabled) {
+    float c, sn;
+    rope_sincos(freqs, s_ + freqs.position_offset, d >> 1, &c, &sn);
+    const float a0 = v.x * c + v.y * sn, a1 = v.y * c - v.x * sn;
+    rope_sincos(freqs, s_ + freqs.position_offset, (d >> 1) + 1, &c, &sn);
+    const float b0 = v.z * c + v.w * sn, b1 = v.w * c - v.z * sn;
+    v = make_float4(a0, a1, b0, b1);
+  }
+  uint2 w;
+  w.x = ptx::pack_bf16(v.x * scale, v.y * scale);
+  w.y = ptx::pack_bf16(v.z * scale, v.w * scale);
   *reinterpret_cast<uint2*>(dq + st.slice(bh) + static_cast<long long>(s_) * st.row + d) = w;
 }
 
@@ -146,7 +158,8 @@ template <int D>
 __global__ void __launch_bounds__(512, 1)
 fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                    const __grid_constant__ CUtensorMap tmap_dq, const BwdParams prm) {
+                    const __grid_constant__ CUtensorMap tmap_dq, const BwdParams prm,
+                    const __grid_constant__ RopeFreqs freqs) {
   using T = BwdTraits<D>;
   using namespace ptx;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -516,6 +529,16 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           for (int c = 0; c < HC / 16; ++c) {
             tmem_ld_x16(t_lane + col + c * 16, ra);
             tmem_wait_ld();
+            if (which && freqs.enabled) {   // dK leaves through the inverse rotary rotation of its key position
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float cs, sn;
+                rope_sincos(freqs, k_row + freqs.position_offset, (half * HC + c * 16) / 2 + j, &cs, &sn);
+                const float g0 = __uint_as_float(ra[2 * j]), g1 = __uint_as_float(ra[2 * j + 1]);
+                ra[2 * j] = __float_as_uint(g0 * cs + g1 * sn);
+                ra[2 * j + 1] = __float_as_uint(g1 * cs - g0 * sn);
+              }
+            }
             if (k_row < S) {
 #pragma unroll
               for (int v4 = 0; v4 < 2; ++v4) {

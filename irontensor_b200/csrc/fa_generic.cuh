@@ -16,6 +16,7 @@
 #include <cstdint>
 
 #include "layout.cuh"
+#include "rope.cuh"
 
 namespace it {
 
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(128)
 fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
                       const ST* __restrict__ d_o, const float* __restrict__ lse, const float* __restrict__ delta,
                       ST* __restrict__ dq, ST* __restrict__ dk, ST* __restrict__ dv, int S, int D, int causal,
-                      float scale, TensorStrides st, TensorStrides skv) {
+                      float scale, TensorStrides st, TensorStrides skv, const __grid_constant__ RopeFreqs freqs) {
   const int lane = threadIdx.x & 31;
   const int r = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5);
   if (r >= S) return;
@@ -414,6 +415,20 @@ fa_bwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
       for (int j = 0; j < 4; ++j) {
         g0[j] = fmaf(ds, b0[j], g0[j]);            // dq += ds * k_x   or   dk += ds * q_x
         if (MODE == 1) g1[j] = fmaf(p, b1[j], g1[j]);   // dv += p * dO_x
+      }
+    }
+  }
+  if (freqs.enabled) {
+    // dQ and dK leave through the inverse rotary rotation of their row's position
+    // (src/shaders/backward/rope.metal:25-62); the two elements of a pair sit in neighbouring lanes.
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int d = lane + 32 * j;
+      const float other = __shfl_xor_sync(0xffffffffu, g0[j], 1);
+      if (d < D) {
+        float c, sn;
+        rope_sincos(freqs, r + freqs.position_offset, d >> 1, &c, &sn);
+        g0[j] = (d & 1) ? (g0[j] * c - other * sn) : (g0[j] * c + other * sn);
       }
     }
   }

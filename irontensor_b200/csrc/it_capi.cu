@@ -17,6 +17,7 @@
 #include <new>
 
 #include "fa_bwd_sm100.cuh"
+#include <algorithm>
 #include <type_traits>
 
 #include "fa_fwd_sm100.cuh"
@@ -98,6 +99,16 @@ it::TensorStrides strides_kv(bool bshd, int64_t H, int64_t Hkv, int64_t S, int64
   return t;
 }
 
+// theta_i = 1 / base^(2i / head_dim) (src/shaders/rope.metal:41-43), in double and rounded once.
+it::RopeFreqs make_rope_freqs(int D, float base, int position_offset, bool enabled) {
+  it::RopeFreqs f;
+  for (int i = 0; i < 64; ++i)
+    f.inv_freq[i] = (enabled && 2 * i < D) ? static_cast<float>(1.0 / pow(static_cast<double>(base), (2.0 * i) / D)) : 0.f;
+  f.enabled = enabled ? 1 : 0;
+  f.position_offset = position_offset;
+  return f;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 it_status check_common(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S, int32_t D) {
@@ -158,7 +169,7 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
 template <typename ST>
 void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
                         const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-                        float* delta, const it::TensorStrides& st, const it::TensorStrides& skv) {
+                        float* delta, const it::TensorStrides& st, const it::TensorStrides& skv, const it::RopeFreqs& rf) {
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
   const ST *oo = static_cast<const ST*>(o), *dd = static_cast<const ST*>(d_o);
@@ -166,9 +177,9 @@ void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
   it::fa_bwd_generic_delta_kernel<ST><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(oo, dd, delta, rows, S, D, st);
   const dim3 grid((S + 3) / 4, BH), grid_kv((S + 3) / 4, BH / skv.group);
   it::fa_bwd_generic_kernel<ST, 0><<<grid, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq), static_cast<ST*>(dk),
-                                                        static_cast<ST*>(dv), S, D, causal, scale, st, skv);
+                                                        static_cast<ST*>(dv), S, D, causal, scale, st, skv, rf);
   it::fa_bwd_generic_kernel<ST, 1><<<grid_kv, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq), static_cast<ST*>(dk),
-                                                           static_cast<ST*>(dv), S, D, causal, scale, st, skv);
+                                                           static_cast<ST*>(dv), S, D, causal, scale, st, skv, rf);
   ctx->launches += 3;
 }
 
@@ -241,7 +252,7 @@ template <int D>
 it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk,
                            void* dv, uint8_t* ws, const BwdWorkspace& w, const it::TensorStrides& stv,
-                           const it::TensorStrides& skv) {
+                           const it::TensorStrides& skv, const it::RopeFreqs& rf) {
   const int BH = B * H;
   const int Hkv = H / skv.group;
   using T = it::BwdTraits<D>;
@@ -293,14 +304,14 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const int n_kt = (S + 127) / 128;
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
-  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p);
+  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p, rf);
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
   }
   const size_t n4 = n_dq / 4;
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
-      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, stv);
+      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, stv, rf);
   ctx->launches += 3;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -568,7 +579,8 @@ it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int3
 static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t Hkv,
                                     int32_t S, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
                                     const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
-                                    void* workspace, size_t workspace_bytes, bool bshd) {
+                                    void* workspace, size_t workspace_bytes, bool bshd,
+                                    const it::RopeFreqs& rf = make_rope_freqs(0, 1.f, 0, false)) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
   if (H > 0 && (st = check_kv_heads(H, Hkv)) != IT_OK) return st;
@@ -591,14 +603,14 @@ static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
   const it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
   if (use_sm100_path(dtype, S, D)) {
     return D == 128
-               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv)
-               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv);
+               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf)
+               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf);
   }
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   if (dtype == IT_F32)
-    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv);
+    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv, rf);
   else
-    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv);
+    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv, rf);
   IT_CUDA(cudaGetLastError());
   return IT_OK;
 }
@@ -624,6 +636,55 @@ it_status it_attention_gqa_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, i
                                void* workspace, size_t workspace_bytes) {
   return attention_bwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
                             workspace_bytes, true);
+}
+
+static it_status check_rope(int32_t D, float base) {
+  if (D < 2 || D > 128 || (D & 1)) return fail(IT_ERR_UNSUPPORTED_SHAPE, "rotary embedding needs an even head_dim in 2..128, got %d", D);
+  if (!(base > 0.f)) return fail(IT_ERR_INVALID_ARG, "rotary base must be positive");
+  return IT_OK;
+}
+
+it_status it_attention_gqa_bwd_rope(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H,
+                                    int32_t Hkv, int32_t D, int32_t causal, float rope_base, int32_t position_offset,
+                                    const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                    const float* lse, void* dq, void* dk, void* dv, void* workspace,
+                                    size_t workspace_bytes) {
+  it_status st = check_rope(D, rope_base);
+  if (st != IT_OK) return st;
+  return attention_bwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
+                            workspace_bytes, true, make_rope_freqs(D, rope_base, position_offset, true));
+}
+
+it_status it_rope_qk(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H, int32_t Hkv,
+                     int32_t D, float rope_base, int32_t position_offset, int32_t inverse, const void* q_in,
+                     const void* k_in, void* q_out, void* k_out) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (dtype != IT_F32 && dtype != IT_BF16) return fail(IT_ERR_PRECISION, "dtype %d is not F32 or BF16", (int)dtype);
+  if (B < 0 || S < 0 || H < 0 || Hkv < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  it_status st = check_rope(D, rope_base);
+  if (st != IT_OK) return st;
+  if (static_cast<int64_t>(B) * S == 0 || H + Hkv == 0) return IT_OK;
+  if (H > 0 && (q_in == nullptr || q_out == nullptr)) return fail(IT_ERR_INVALID_ARG, "null q tensor");
+  if (Hkv > 0 && (k_in == nullptr || k_out == nullptr)) return fail(IT_ERR_INVALID_ARG, "null k tensor");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  const it::RopeFreqs rf = make_rope_freqs(D, rope_base, position_offset, true);
+  const int half = D / 2;
+  const int n_heads = H + Hkv;
+  const int threads = half * std::max(1, std::min(n_heads, 256 / half));
+  const unsigned grid = static_cast<unsigned>(static_cast<int64_t>(B) * S);
+  const void* kin = Hkv > 0 ? k_in : nullptr;
+#define IT_ROPE_LAUNCH(ST, INV)                                                                                   \
+  it::rope_qk_kernel<ST, INV><<<grid, threads, 0, stream->s>>>(static_cast<const ST*>(q_in), static_cast<const ST*>(kin), \
+                                                               static_cast<ST*>(q_out), static_cast<ST*>(k_out), S, H, Hkv, D, rf)
+  if (dtype == IT_F32) {
+    if (inverse) IT_ROPE_LAUNCH(float, true); else IT_ROPE_LAUNCH(float, false);
+  } else {
+    if (inverse) IT_ROPE_LAUNCH(__nv_bfloat16, true); else IT_ROPE_LAUNCH(__nv_bfloat16, false);
+  }
+#undef IT_ROPE_LAUNCH
+  ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
 }
 
 // Scratch for it_flash_attention_bwd_noalloc: part of the module image on every GPU that loads it.

@@ -308,6 +308,19 @@ class raw:
                                               lse, dq, dk, dv, ws, ws_bytes))
 
     @staticmethod
+    def rope_qk(dtype, B, S, H, Hkv, D, base, position_offset, inverse, q_in, k_in, q_out, k_out, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_rope_qk(c.handle, c.stream(), dtype, B, S, H, Hkv, D, float(base), int(position_offset),
+                                    int(inverse), q_in, k_in, q_out, k_out))
+
+    @staticmethod
+    def bwd_gqa_rope(dtype, B, S, H, Hkv, D, causal, base, position_offset, q, k, v, o, d_o, lse, dq, dk, dv, ws, ws_bytes,
+                     ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_gqa_bwd_rope(c.handle, c.stream(), dtype, B, S, H, Hkv, D, int(causal), float(base),
+                                                   int(position_offset), q, k, v, o, d_o, lse, dq, dk, dv, ws, ws_bytes))
+
+    @staticmethod
     def bwd_workspace_bytes(dtype, B, H, S, D):
         n = ctypes.c_size_t()
         _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))
@@ -435,10 +448,35 @@ def attention_gqa(q, k, v, causal=True):
     return out
 
 
-def attention_gqa_backward(grad_output, q, k, v, o, causal=True):
+def rope(input, base=10000.0, position_offset=0):
+    """Rotary position embedding of one [batch, seq, heads, head_dim] tensor (src/ops/rope.rs:22-75)."""
+    assert len(input.shape()) == 4, "Input must be 4D [batch, seq_len, num_heads, head_dim]"
+    B, S, H, D = input.shape()
+    assert D % 2 == 0, "head_dim must be even for RoPE"
+    out = Tensor.empty([B, S, H, D], input.precision())
+    raw.rope_qk(_dtype_code(input.precision()), B, S, H, 0, D, base, position_offset, False, input.data_ptr(), None,
+                out.data_ptr(), None)
+    return out
+
+
+def rope_qk(q, k, base=10000.0, position_offset=0, inverse=False):
+    """rope(q) and rope(k) (src/train/forward.rs:111-112) as one launch; k may have fewer heads.  `inverse`
+    gives the backward rotation (rope_backward, src/ops/backward/rope.rs)."""
+    B, S, H, D = q.shape()
+    Hkv = k.shape()[2]
+    assert k.shape() == [B, S, Hkv, D] and k.precision() is q.precision() and D % 2 == 0
+    qo, ko = Tensor.empty([B, S, H, D], q.precision()), Tensor.empty([B, S, Hkv, D], q.precision())
+    raw.rope_qk(_dtype_code(q.precision()), B, S, H, Hkv, D, base, position_offset, inverse, q.data_ptr(), k.data_ptr(),
+                qo.data_ptr(), ko.data_ptr())
+    return qo, ko
+
+
+def attention_gqa_backward(grad_output, q, k, v, o, causal=True, rope_base=None, position_offset=0):
     """(dQ, dK, dV) for attention_gqa(): dQ like q, dK and dV like k and v, i.e. already summed over the query
     heads of each group (the reference's repeat_kv_backward after its attention backward,
-    src/train/backward.rs:102-122; src/ops/repeat_kv.rs:151-232)."""
+    src/train/backward.rs:102-122; src/ops/repeat_kv.rs:151-232).  With `rope_base`, q and k are the rotated
+    tensors the forward attended over and dQ, dK come back as gradients of the un-rotated ones: the
+    reference's two rope_backward passes (src/train/backward.rs:129,132) folded into this call."""
     p = q.precision()
     B, S, H, D = q.shape()
     Hkv = k.shape()[2]
@@ -451,8 +489,12 @@ def attention_gqa_backward(grad_output, q, k, v, o, causal=True):
     code = _dtype_code(p)
     nbytes = raw.bwd_workspace_bytes(code, B, H, S, D)
     ws = _workspace(nbytes)
-    raw.bwd_gqa(code, B, S, H, Hkv, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                grad_output.data_ptr(), o.lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
+    args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(), o.lse.data_ptr(), dq.data_ptr(),
+            dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel())
+    if rope_base is None:
+        raw.bwd_gqa(code, B, S, H, Hkv, D, causal, *args)
+    else:
+        raw.bwd_gqa_rope(code, B, S, H, Hkv, D, causal, rope_base, position_offset, *args)
     return dq, dk, dv
 
 

@@ -133,3 +133,23 @@ def gqa_bwd(q, k, v, d_o, causal=True):
             acc += g5[:, :, r]
         return np.ascontiguousarray(acc.transpose(0, 2, 1, 3))
     return np.ascontiguousarray(dq.transpose(0, 2, 1, 3)), fold(dk), fold(dv)
+
+
+def rope(x, base=10000.0, position_offset=0, inverse=False):
+    """CPU restatement of rope_f32 / rope_backward_f32 (src/shaders/rope.metal:22-61,
+    src/shaders/backward/rope.metal:25-62) on [B,S,H,D], fp32 arithmetic: theta_i = 1 / base^(2i/D),
+    angle = float(position) * theta_i.  theta is rounded once from double, as the library's table is."""
+    x = np.asarray(x, np.float32)
+    B, S, H, D = x.shape
+    i = np.arange(D // 2)
+    theta = (1.0 / np.power(np.float64(base), (2.0 * i) / D)).astype(np.float32)
+    pos = (np.arange(S) + position_offset).astype(np.float32)
+    ang = (pos[:, None] * theta[None, :]).astype(np.float32)          # [S, D/2], the fp32 product
+    c, s = np.cos(ang).astype(np.float32)[None, :, None, :], np.sin(ang).astype(np.float32)[None, :, None, :]
+    if inverse:
+        s = -s
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    out = np.empty_like(x)
+    out[..., 0::2] = x0 * c - x1 * s
+    out[..., 1::2] = x0 * s + x1 * c
+    return out

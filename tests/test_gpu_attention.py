@@ -453,3 +453,59 @@ def test_grouped_query_attention(it_ctx, shape, bf16, causal):
             check_bf16(g / scale, want / scale, f"{shape} {name}")
         else:
             assert np.abs(g - want).max() <= F32_TOL, f"{shape} {name}: {np.abs(g - want).max()}"
+
+
+@pytest.mark.parametrize("shape,bf16,offset", [((1, 2, 1, 4), False, 0), ((2, 16, 8, 64), False, 0), ((1, 8, 4, 32), False, 10),
+                                               ((2, 300, 6, 128), False, 0), ((1, 100, 4, 64), True, 3)])
+def test_rope_matches_reference_math(it_ctx, shape, bf16, offset):
+    """rope() and the one-launch rope_qk() against the CPU restatement of rope_f32 (src/shaders/rope.metal:22-61); the
+    shapes are those of the reference's tests (src/ops/rope.rs:128-250: simple, position zero, larger, with offset)."""
+    from irontensor_b200 import Tensor, rope, rope_qk
+    B, S, H, D = shape
+    x = seeded(140, B, H, S, D, bf16=bf16)[0].transpose(0, 2, 1, 3).copy()     # [B,S,H,D]
+    mk = Tensor.from_f32_as_bf16 if bf16 else Tensor.from_f32_slice
+    tol = 2e-2 if bf16 else 1e-5
+    y = rope(mk(x.reshape(-1), [B, S, H, D]), 10000.0, offset).to_f32_host()
+    assert np.abs(y - ol.rope(x, 10000.0, offset)).max() <= tol
+    if offset == 0 and not bf16:
+        assert np.array_equal(y[:, 0], x[:, 0])                               # position 0 is the identity
+    Hkv = max(1, H // 2)
+    k = x[:, :, :Hkv].copy()
+    qo, ko = rope_qk(mk(x.reshape(-1), [B, S, H, D]), mk(k.reshape(-1), [B, S, Hkv, D]), 10000.0, offset)
+    assert np.abs(qo.to_f32_host() - ol.rope(x, 10000.0, offset)).max() <= tol
+    assert np.abs(ko.to_f32_host() - ol.rope(k, 10000.0, offset)).max() <= tol
+    back, _ = rope_qk(qo, ko, 10000.0, offset, inverse=True)
+    assert np.abs(back.to_f32_host() - x).max() <= (4e-2 if bf16 else 1e-5)
+
+
+@pytest.mark.parametrize("shape,bf16", [((1, 40, 4, 2, 16), False), ((1, 300, 4, 4, 64), False), ((1, 256, 4, 2, 64), True),
+                                        ((1, 384, 4, 1, 128), True)])
+def test_attention_backward_with_rope_folded_in(it_ctx, shape, bf16):
+    """rope -> grouped-query attention -> backward with the rotary backward folded into the kernels' output paths,
+    against the reference's chain rope, repeat_kv, attention, attention backward, repeat_kv_backward, rope_backward
+    (src/train/forward.rs:111-139, src/train/backward.rs:102-132)."""
+    from irontensor_b200 import Tensor, attention_gqa, attention_gqa_backward, rope_qk
+    B, S, H, Hkv, D = shape
+    base, offset = 10000.0, 0
+    q4, _, _, do4 = seeded(150, B, H, S, D, bf16=bf16)
+    _, k4, v4, _ = seeded(151, B, Hkv, S, D, bf16=bf16)
+    to_bshd = lambda a: np.ascontiguousarray(a.transpose(0, 2, 1, 3))
+    q, k, v, d_o = (to_bshd(a) for a in (q4, k4, v4, do4))
+    mk = Tensor.from_f32_as_bf16 if bf16 else Tensor.from_f32_slice
+    tq, tk, tv, tdo = mk(q.reshape(-1), [B, S, H, D]), mk(k.reshape(-1), [B, S, Hkv, D]), mk(v.reshape(-1), [B, S, Hkv, D]), \
+        mk(d_o.reshape(-1), [B, S, H, D])
+    tqr, tkr = rope_qk(tq, tk, base, offset)
+    o = attention_gqa(tqr, tkr, tv, True)
+    dq, dk, dv = attention_gqa_backward(tdo, tqr, tkr, tv, o, True, rope_base=base, position_offset=offset)
+    assert it_ctx.poll_status() == 0
+    # oracle: rotate what the device rotated (its stored, rounded q_rope/k_rope), so that only the backward is compared
+    qr, kr = tqr.to_f32_host(), tkr.to_f32_host()
+    rdq, rdk, rdv = ol.gqa_bwd(qr, kr, v, d_o, True)
+    rdq, rdk = ol.rope(rdq, base, offset, inverse=True), ol.rope(rdk, base, offset, inverse=True)
+    for got, want, name in ((dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        g = got.to_f32_host()
+        if bf16:
+            scale = math.sqrt(H // Hkv) if name in ("dK", "dV") else 1.0
+            check_bf16(g / scale, want / scale, f"{shape} {name}")
+        else:
+            assert np.abs(g - want).max() <= F32_TOL, f"{shape} {name}: {np.abs(g - want).max()}"

@@ -1,6 +1,7 @@
 """CPU tests of the oracle itself: against the golden vectors produced by the reference's own
 shader sources, against those sources directly where oracle/_ref was built, against an independent
 fp64 formulation and finite differences, and of the bf16 rounding rule."""
+import math
 import os
 
 import numpy as np
@@ -189,3 +190,24 @@ def test_generator_is_counter_based():
     assert not np.array_equal(full[0], full[1])
     h = synth.attention_inputs(5, 2, 3, 16, 8, bf16=True, qk_scale=0.5)
     assert np.array_equal(h[0], synth.round_bf16(h[0]))
+
+
+def test_rope_oracle_against_reference_unit_values():
+    """The reference's own checks for rope (src/ops/rope.rs tests): position 0 is the identity, the rotation keeps
+    the norm of every pair, a quarter turn maps (1, 0) to (0, 1), and backward(forward(x)) = x."""
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((2, 7, 3, 8)).astype(np.float32)
+    y = ol.rope(x)
+    assert np.array_equal(y[:, 0], x[:, 0])                                    # position 0: angle 0
+    n_in = x[..., 0::2] ** 2 + x[..., 1::2] ** 2
+    n_out = y[..., 0::2] ** 2 + y[..., 1::2] ** 2
+    assert np.abs(n_in - n_out).max() < 1e-5
+    assert np.abs(ol.rope(y, inverse=True) - x).max() < 1e-5
+    # pair 0 has theta = 1: at position p the angle is p radians
+    e = np.zeros((1, 3, 1, 4), np.float32)
+    e[..., 0] = 1.0
+    r = ol.rope(e)
+    for p in range(3):
+        assert abs(r[0, p, 0, 0] - math.cos(p)) < 1e-6 and abs(r[0, p, 0, 1] - math.sin(p)) < 1e-6
+    # position offset shifts the angle
+    assert np.allclose(ol.rope(e, position_offset=2)[0, 0, 0, :2], [math.cos(2), math.sin(2)], atol=1e-6)
