@@ -44,7 +44,7 @@ METRIC = "causal attention fwd+bwd TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of fa_bwd_sm100_kernel from an ncu capture:
 # profiles/fa_bwd_sm100_c4_32slices_ncu.md measured 0.405 GB + 0.225 GB on 32 of the 64 slices; traffic
 # grows in proportion to the slices a launch processes, so the full launch is twice that.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c4": 2 * (405.263360e6 + 224.876544e6)}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c4": 2 * (405.279744e6 + 225.147648e6)}
 
 def flops_fwd(bh, S, D):
     return 2.0 * bh * S * S * D
