@@ -165,6 +165,22 @@ it_status it_attention_gqa_bwd_rope(it_ctx* ctx, it_stream* stream, it_dtype dty
                                     const void* v, const void* o, const void* d_o, const float* lse, void* dq,
                                     void* dk, void* dv, void* workspace, size_t workspace_bytes);
 
+/* Attention for ONE new token per sequence against a key/value cache.  (The reference has no cache: its
+ * generator re-runs the whole forward for every generated token, src/inference/generator.rs:146-200, and
+ * lists "Inference-optimized KV cache" as future work, docs/PRESENTATION.md:576.)  q, o: [batch, heads,
+ * head_dim]; k_cache, v_cache: [batch, max_len, kv_heads, head_dim] (the [B,S,H,D] layout the projections
+ * produce, so appending a token writes one row), of which the first kv_len positions are valid and include
+ * the new token's own key and value; kv_heads divides heads.  o equals the last row of causal attention
+ * over those kv_len tokens (src/shaders/flash_attention.metal:167-223 with q = kv_len - 1); lse ([batch,
+ * heads], natural log, may be null) as in it_flash_attention_fwd.  The keys are split over CTAs and merged
+ * when batch * kv_heads alone cannot fill the GPU; each cache row is read once per group of query heads.
+ * head_dim a multiple of 8.  workspace: it_attention_decode_workspace_bytes, 256-byte aligned. */
+it_status it_attention_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, size_t* out_bytes);
+it_status it_attention_decode(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t heads,
+                              int32_t kv_heads, int32_t head_dim, int32_t kv_len, int32_t max_len, const void* q,
+                              const void* k_cache, const void* v_cache, void* o, float* lse, void* workspace,
+                              size_t workspace_bytes);
+
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)
  *

@@ -52,6 +52,8 @@ SIGNATURES = {
     "it_rope_qk": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _c.c_float, _i32, _i32, _vp, _vp, _vp, _vp],
     "it_attention_gqa_bwd_rope": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _c.c_float, _i32] + [_vp] * 9 +
                                  [_vp, _c.c_size_t],
+    "it_attention_decode_workspace_bytes": [_i32, _i32, _i32, _c.POINTER(_c.c_size_t)],
+    "it_attention_decode": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_size_t],
     "it_flash_attention_bwd_noalloc": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9,
     "it_attention_status_poll": [_vp, _vp, _c.POINTER(_i32)],
     "it_ctx_launch_count": [_vp, _c.POINTER(_c.c_uint64)],

@@ -21,6 +21,7 @@
 #include <type_traits>
 
 #include "fa_fwd_sm100.cuh"
+#include "fa_decode.cuh"
 #include "fa_fwd_pp_sm100.cuh"
 #include "fa_generic.cuh"
 #include "selftest_sm100.cuh"
@@ -313,6 +314,52 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
       dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, stv, rf);
   ctx->launches += 3;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+constexpr int kDecodeMaxSplits = 64;
+
+template <typename ST>
+it_status launch_decode(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv, int D, int kv_len, int max_len,
+                               const void* q, const void* kc, const void* vc, void* o, float* lse, float* ws) {
+  const int G = H / Hkv;
+  const int chunks = (G + it::DEC_GC - 1) / it::DEC_GC;
+  const long long base_ctas = static_cast<long long>(B) * Hkv * chunks;
+  // enough CTAs for about four per SM, no split shorter than 256 keys, at most kDecodeMaxSplits
+  long long want = (4LL * ctx->sm_count + base_ctas - 1) / base_ctas;
+  want = std::max(1LL, std::min<long long>({want, (kv_len + 255) / 256, kDecodeMaxSplits}));
+  int split_len = static_cast<int>((kv_len + want - 1) / want);
+  split_len = (split_len + it::DEC_TK - 1) / it::DEC_TK * it::DEC_TK;
+  const int n_splits = (kv_len + split_len - 1) / split_len;
+  it::DecodeParams p;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.D = D;
+  p.kv_len = kv_len;
+  p.cache_batch_stride = static_cast<long long>(max_len) * Hkv * D;
+  p.n_splits = n_splits;
+  p.split_len = split_len;
+  p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
+  const int pad = 16 / static_cast<int>(sizeof(ST));
+  const size_t smem = static_cast<size_t>(it::DEC_GC) * D * 4 + 2ull * it::DEC_TK * (D + pad) * sizeof(ST) +
+                      static_cast<size_t>(it::DEC_GC) * it::DEC_TK * 4 + 3 * it::DEC_GC * 4;
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    IT_CUDA(cudaFuncSetAttribute(it::fa_decode_split_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    attr_set[ctx->device & 15] = true;
+  }
+  float* part_o = ws;
+  float* part_ml = ws + static_cast<size_t>(B) * H * n_splits * D;
+  const dim3 grid(n_splits, B * Hkv, chunks);
+  it::fa_decode_split_kernel<ST><<<grid, it::DEC_THREADS, smem, s>>>(
+      static_cast<const ST*>(q), static_cast<const ST*>(kc), static_cast<const ST*>(vc), static_cast<ST*>(o), lse, part_o,
+      part_ml, p);
+  ctx->launches += 1;
+  if (n_splits > 1) {
+    it::fa_decode_merge_kernel<ST><<<B * H, 128, 0, s>>>(part_o, part_ml, static_cast<ST*>(o), lse, n_splits, D);
+    ctx->launches += 1;
+  }
   IT_CUDA(cudaGetLastError());
   return IT_OK;
 }
@@ -685,6 +732,39 @@ it_status it_rope_qk(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, 
   ctx->launches += 1;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
+}
+
+it_status it_attention_decode_workspace_bytes(int32_t B, int32_t H, int32_t D, size_t* out_bytes) {
+  if (out_bytes == nullptr) return fail(IT_ERR_INVALID_ARG, "out_bytes is null");
+  if (B < 0 || H < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  if (D < 1 || D > 128) return fail(IT_ERR_UNSUPPORTED_SHAPE, "head_dim must be in 1..128, got %d", D);
+  const size_t n = static_cast<size_t>(B) * H * kDecodeMaxSplits * (static_cast<size_t>(D) + 2) * sizeof(float);
+  *out_bytes = (n + 255) / 256 * 256 + 256;
+  return IT_OK;
+}
+
+it_status it_attention_decode(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t Hkv,
+                              int32_t D, int32_t kv_len, int32_t max_len, const void* q, const void* k_cache,
+                              const void* v_cache, void* o, float* lse, void* workspace, size_t workspace_bytes) {
+  it_status st = check_common(ctx, stream, dtype, B, H, 0, D);
+  if (st != IT_OK) return st;
+  if (H > 0 && (st = check_kv_heads(H, Hkv)) != IT_OK) return st;
+  if (kv_len < 1 || max_len < kv_len) return fail(IT_ERR_INVALID_ARG, "need 1 <= kv_len <= max_len, got %d, %d", kv_len, max_len);
+  if (D % 8 != 0) return fail(IT_ERR_UNSUPPORTED_SHAPE, "decode needs head_dim a multiple of 8, got %d", D);
+  if (B == 0 || H == 0) return IT_OK;
+  if (q == nullptr || k_cache == nullptr || v_cache == nullptr || o == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(o))
+    return fail(IT_ERR_ALIGNMENT, "q, caches and o must be 16-byte aligned");
+  size_t need = 0;
+  it_attention_decode_workspace_bytes(B, H, D, &need);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(IT_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(IT_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  float* ws = static_cast<float*>(workspace);
+  return dtype == IT_F32 ? launch_decode<float>(ctx, stream->s, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o, lse, ws)
+                         : launch_decode<__nv_bfloat16>(ctx, stream->s, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o,
+                                                        lse, ws);
 }
 
 // Scratch for it_flash_attention_bwd_noalloc: part of the module image on every GPU that loads it.

@@ -321,6 +321,18 @@ class raw:
                                                    int(position_offset), q, k, v, o, d_o, lse, dq, dk, dv, ws, ws_bytes))
 
     @staticmethod
+    def decode_workspace_bytes(B, H, D):
+        out = ctypes.c_size_t(0)
+        _lib.check(_lib.load().it_attention_decode_workspace_bytes(B, H, D, ctypes.byref(out)))
+        return out.value
+
+    @staticmethod
+    def decode(dtype, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o, lse, ws, ws_bytes, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_decode(c.handle, c.stream(), dtype, B, H, Hkv, D, kv_len, max_len, q, k_cache,
+                                             v_cache, o, lse, ws, ws_bytes))
+
+    @staticmethod
     def bwd_workspace_bytes(dtype, B, H, S, D):
         n = ctypes.c_size_t()
         _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))
@@ -496,6 +508,26 @@ def attention_gqa_backward(grad_output, q, k, v, o, causal=True, rope_base=None,
     else:
         raw.bwd_gqa_rope(code, B, S, H, Hkv, D, causal, rope_base, position_offset, *args)
     return dq, dk, dv
+
+
+def attention_decode(q, k_cache, v_cache, kv_len):
+    """Attention of one new token per sequence against a key/value cache: q [batch, heads, head_dim], caches
+    [batch, max_len, kv_heads, head_dim] whose first `kv_len` positions are valid (the new token's key and value
+    included).  Equals the last row of the causal attention the reference's generator recomputes from scratch for
+    every token (src/inference/generator.rs:146-200).  The result carries `.lse` ([batch, heads])."""
+    p = q.precision()
+    assert k_cache.precision() is p and v_cache.precision() is p
+    assert len(q.shape()) == 3 and len(k_cache.shape()) == 4 and k_cache.shape() == v_cache.shape()
+    B, H, D = q.shape()
+    Bc, max_len, Hkv, Dc = k_cache.shape()
+    assert Bc == B and Dc == D and H % Hkv == 0 and 1 <= kv_len <= max_len
+    out = Tensor.empty([B, H, D], p)
+    out.lse = Tensor.empty([B, H], Precision.FP32)
+    nbytes = raw.decode_workspace_bytes(B, H, D)
+    ws = _workspace(nbytes)
+    raw.decode(_dtype_code(p), B, H, Hkv, D, kv_len, max_len, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+               out.data_ptr(), out.lse.data_ptr(), ws.data_ptr(), ws.numel())
+    return out
 
 
 def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=True):

@@ -509,3 +509,49 @@ def test_attention_backward_with_rope_folded_in(it_ctx, shape, bf16):
             check_bf16(g / scale, want / scale, f"{shape} {name}")
         else:
             assert np.abs(g - want).max() <= F32_TOL, f"{shape} {name}: {np.abs(g - want).max()}"
+
+
+@pytest.mark.parametrize("shape,bf16", [((2, 4, 4, 64, 100, 128), False), ((1, 8, 2, 128, 1000, 1024), False),
+                                        ((3, 6, 2, 64, 777, 800), True), ((2, 32, 4, 128, 5000, 5000), True),
+                                        ((1, 16, 1, 128, 4096, 4096), True), ((16, 4, 4, 64, 64, 256), True),
+                                        ((1, 2, 2, 40, 333, 400), False)])
+def test_kv_cache_decode_equals_last_row_of_causal_attention(it_ctx, shape, bf16):
+    """attention_decode (one new token against a K/V cache, grouped heads, keys split over CTAs) against the
+    last row of the oracle's causal attention over the same kv_len tokens."""
+    from irontensor_b200 import Tensor, attention_decode
+    B, H, Hkv, D, L, max_len = shape
+    q4, _, _, _ = seeded(160, B, H, L, D, bf16=bf16)          # [B,H,L,D]; only the last row matters
+    _, k4, v4, _ = seeded(161, B, Hkv, L, D, bf16=bf16)
+    mk = Tensor.from_f32_as_bf16 if bf16 else Tensor.from_f32_slice
+    kc = np.zeros((B, max_len, Hkv, D), np.float32)
+    vc = np.full((B, max_len, Hkv, D), 7.0, np.float32)       # positions past kv_len must not be read into the result
+    kc[:, :L] = k4.transpose(0, 2, 1, 3)
+    vc[:, :L] = v4.transpose(0, 2, 1, 3)
+    q_last = np.ascontiguousarray(q4[:, :, L - 1])            # [B,H,D]
+    out = attention_decode(mk(q_last.reshape(-1), [B, H, D]), mk(kc.reshape(-1), [B, max_len, Hkv, D]),
+                           mk(vc.reshape(-1), [B, max_len, Hkv, D]), L)
+    assert it_ctx.poll_status() == 0
+    G = H // Hkv
+    ro, rlse = ol.fwd(q4, np.repeat(k4, G, axis=1), np.repeat(v4, G, axis=1), True)
+    tol = BF16_MAX_ABS if bf16 else F32_TOL
+    assert np.abs(out.to_f32_host() - ro[:, :, L - 1]).max() <= tol
+    assert np.abs(out.lse.to_f32_host() - rlse[:, :, L - 1]).max() <= 1e-4
+
+
+def test_kv_cache_decode_over_a_generation(it_ctx):
+    """The reference's greedy generation pattern (config 5: B1 H4 D64, sequence lengths 20..119, one full forward per
+    token, src/inference/generator.rs:146-200) served from a cache: every step's decode output equals the last row of
+    the full forward at that length."""
+    from irontensor_b200 import Tensor, attention_decode, flash_attention
+    B, H, D, L0, L1 = 1, 4, 64, 20, 120
+    q, k, v, _ = seeded(synth.BASE_SEED + 5, B, H, L1, D)
+    kc = Tensor.from_f32_slice(np.ascontiguousarray(k.transpose(0, 2, 1, 3)).reshape(-1), [B, L1, H, D])
+    vc = Tensor.from_f32_slice(np.ascontiguousarray(v.transpose(0, 2, 1, 3)).reshape(-1), [B, L1, H, D])
+    worst = 0.0
+    for L in range(L0, L1):
+        full = flash_attention(*(Tensor.from_f32_slice(np.ascontiguousarray(x[:, :, :L]).reshape(-1), [B, H, L, D]) for x in (q, k, v)), True)
+        want = full.to_f32_host()[:, :, L - 1]
+        got = attention_decode(Tensor.from_f32_slice(np.ascontiguousarray(q[:, :, L - 1]).reshape(-1), [B, H, D]), kc, vc, L)
+        worst = max(worst, float(np.abs(got.to_f32_host() - want).max()))
+    assert it_ctx.poll_status() == 0
+    assert worst <= F32_TOL, worst
