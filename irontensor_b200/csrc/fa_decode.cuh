@@ -16,6 +16,9 @@
 //     score pass (16-byte reads down a column of rows) and the lane-per-dimension output pass are free
 //     of bank conflicts; several CTAs per SM hide the load latency.
 // CUDA cores, fp32 math in the exp2 domain; bf16 or fp32 storage; D a multiple of 8, at most 128.
+// This file is the general path.  bf16 caches with head_dim 64 or 128 and at least 256 positions go through
+// the tensor-core pipeline instead (fa_fwd_pp_sm100.cuh, DECODE), which streams the cache by TMA and is
+// several times faster; both leave the same partial results for fa_decode_merge_kernel.
 #pragma once
 #include <cuda_bf16.h>
 

@@ -61,7 +61,14 @@ struct FwdPPTraits {
 };
 
 
-template <int D>
+// DECODE = true is the same pipeline for one new token per sequence against a key/value cache
+// (fa_decode.cuh describes the op): the rows of the query tile are the query HEADS of one K/V head's
+// group (rows past the group are zero-filled by TMA and never stored), prm.S is the number of valid
+// cache positions, a CTA takes one split of the key tiles of one (batch, K/V head) and leaves either
+// the final output (one split) or an unnormalised partial output with its reference maximum and row
+// sum for fa_decode_merge_kernel.  The cache is streamed by TMA through the same K and V rings, so
+// the op runs at the rate the memory system delivers tiles, not at the rate CUDA cores can issue loads.
+template <int D, bool DECODE = false>
 __global__ void __launch_bounds__(384, 1)
 fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FwdParams prm) {
@@ -95,11 +102,26 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int n_qt = (S + T::BM - 1) / T::BM;
   // Head-major order: the CTAs resident at one time belong to a few (batch, head) slices, so the K/V
   // tiles they all stream stay in L2.  Within a slice the last query tiles (most keys) go first.
-  const int bh = static_cast<int>(blockIdx.x) / n_qt;
-  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x) % n_qt;
-  const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
-  const int hkv = hd / prm.kv_group;                          // the K/V head this query head reads
-  const int nkv = prm.causal ? min(qt + 1, n_kv_total) : n_kv_total;
+  int bh, qt, hd, bt, hkv, nkv, j0 = 0;   // j0: first key tile of this CTA (decode splits)
+  if (DECODE) {
+    const int kv_heads = prm.st.heads / prm.kv_group;
+    const int bkv = static_cast<int>(blockIdx.x) / prm.dec_n_splits;   // batch * kv_heads + kv_head
+    const int sp = static_cast<int>(blockIdx.x) % prm.dec_n_splits;
+    hkv = bkv % kv_heads;
+    bt = bkv / kv_heads;
+    hd = hkv;                      // the query tensor map is [D, group, kv_heads, batch]
+    qt = 0;
+    bh = bt * prm.st.heads + hkv * prm.kv_group;   // first query slice of the group
+    j0 = sp * prm.dec_tiles_per_split;
+    nkv = max(0, min(prm.dec_tiles_per_split, n_kv_total - j0));
+  } else {
+    bh = static_cast<int>(blockIdx.x) / n_qt;
+    qt = n_qt - 1 - static_cast<int>(blockIdx.x) % n_qt;
+    hd = bh % prm.st.heads;   // TMA coordinates of the slice
+    bt = bh / prm.st.heads;
+    hkv = hd / prm.kv_group;  // the K/V head this query head reads
+    nkv = prm.causal ? min(qt + 1, n_kv_total) : n_kv_total;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -135,7 +157,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const bool bad_start = (*abort_flag != 0);
+  const bool bad_start = (*abort_flag != 0) || nkv <= 0;   // an empty split (the launcher makes none) must not wait
 
   // Register budget: the control warpgroup keeps 80 per thread, the two softmax warpgroups take
   // 208 each so that a whole 128-column row of S stays in registers (128*80 + 256*208 = 63488).
@@ -159,7 +181,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
-                        i * T::BN, hkv, bt);
+                        (j0 + i) * T::BN, hkv, bt);
         }
       }
     } else if (warp == 3) {
@@ -174,7 +196,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
           for (int b = 0; b < T::NBLK; ++b)
             tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
-                        i * T::BN, hkv, bt);
+                        (j0 + i) * T::BN, hkv, bt);
         }
       }
     } else if (warp == 1) {
@@ -243,7 +265,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const uint32_t t_o = t_lane + T::COL_O;
       const uint32_t t_p = t_lane + T::COL_P;
       const float sl2 = prm.scale_log2;
-      const int k_limit = prm.causal ? min(S - 1, q_row) : (S - 1);   // last visible key index
+      const int k_limit = (!DECODE && prm.causal) ? min(S - 1, q_row) : (S - 1);   // last visible key index
       float m_used = -INFINITY;   // the reference this group's partial sum is relative to
       float l_sum = 0.f;
       bool ok = true;
@@ -284,8 +306,8 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&s_free[w]);   // the S buffer may take S(j+2)
-        if ((prm.causal && j == qt) || ((j + 1) * T::BN > S)) {   // diagonal or ragged last tile
-          const int vis = k_limit - j * T::BN;   // columns 0..vis are visible
+        if ((!DECODE && prm.causal && j == qt) || ((j0 + j + 1) * T::BN > S)) {   // diagonal or ragged last tile
+          const int vis = k_limit - (j0 + j) * T::BN;   // columns 0..vis are visible
 #pragma unroll
           for (int i = 0; i < 128; ++i)
             if (i > vis) r[i] = 0xFF800000u;     // -inf: drops out of the max, exp2 gives 0
@@ -397,7 +419,43 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                        DEV_ERR_TIMEOUT_MMA);   // last P V complete
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) {
+      if (ok && DECODE) {
+        // rows are the query heads of the group; this group stores half of the columns of each
+        tc_fence_after();
+        const float l_tot = l_part[row] + l_part[128 + row];
+        constexpr int HC = D / 2;
+#pragma unroll
+        for (int c = 0; c < HC / 32; ++c)
+          tmem_ld_x32(t_o + w * HC + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tmem_wait_ld();
+        if (row < prm.kv_group) {
+          const size_t slice = static_cast<size_t>(bh) + row;
+          if (prm.dec_n_splits == 1) {
+            const float inv_l = 1.0f / l_tot;
+            __nv_bfloat16* orow = prm.o + slice * D + w * HC;
+#pragma unroll
+            for (int v = 0; v < HC / 8; ++v) {
+              uint4 o4;
+              o4.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
+              o4.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
+              o4.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
+              o4.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + v * 8) = o4;
+            }
+            if (w == 0 && prm.lse != nullptr) prm.lse[slice] = (m_fin + lg2(l_tot)) * 0.6931471805599453f;
+          } else {
+            const int sp = static_cast<int>(blockIdx.x) % prm.dec_n_splits;
+            float* prow = prm.dec_part_o + (slice * prm.dec_n_splits + sp) * D + w * HC;
+#pragma unroll
+            for (int v = 0; v < HC / 4; ++v)
+              *reinterpret_cast<uint4*>(prow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+            if (w == 0) {
+              prm.dec_part_ml[(slice * prm.dec_n_splits + sp) * 2] = m_fin;
+              prm.dec_part_ml[(slice * prm.dec_n_splits + sp) * 2 + 1] = l_tot;
+            }
+          }
+        }
+      } else if (ok) {
         tc_fence_after();
         const float l_tot = l_part[row] + l_part[128 + row];
         const float inv_l = 1.0f / l_tot;

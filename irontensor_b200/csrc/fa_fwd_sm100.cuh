@@ -55,6 +55,11 @@ struct FwdParams {
   int causal;
   float scale_log2;     // 1/sqrt(D) * log2(e)
   int kv_group;         // query heads per K/V head (grouped-query attention; 1 otherwise)
+  // decode instantiation of the long-sequence kernel only (one new token against a key/value cache):
+  int dec_tiles_per_split;   // key tiles per CTA
+  int dec_n_splits;
+  float* dec_part_o;    // [B*H, n_splits, D] unnormalised partial outputs (n_splits > 1)
+  float* dec_part_ml;   // [B*H, n_splits, 2] reference maximum (log2 domain) and row sum of each split
 };
 
 template <int D>

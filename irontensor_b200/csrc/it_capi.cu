@@ -215,6 +215,10 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
   p.kv_group = skv.group;
+  p.dec_tiles_per_split = 0;
+  p.dec_n_splits = 1;
+  p.dec_part_o = nullptr;
+  p.dec_part_ml = nullptr;
   const int n_ctas_per_slice = (S + T::BM * T::QT_PER_CTA - 1) / (T::BM * T::QT_PER_CTA);
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
   kernel<<<static_cast<unsigned>(n_ctas_per_slice) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
@@ -319,6 +323,58 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
 }
 
 constexpr int kDecodeMaxSplits = 64;
+
+// Decode on the tensor-core pipeline (bf16, head_dim 64 or 128): the group's query heads are the rows of
+// one query tile, the cache is streamed by TMA.  See fa_fwd_pp_sm100.cuh, DECODE.
+template <int D>
+it_status launch_decode_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv, int kv_len, int max_len, const void* q,
+                              const void* kc, const void* vc, void* o, float* lse, float* ws) {
+  using T = it::FwdPPTraits<D>;
+  const int G = H / Hkv;
+  const int n_tiles = (kv_len + T::BN - 1) / T::BN;
+  const long long base_ctas = static_cast<long long>(B) * Hkv;
+  // one CTA per SM runs at a time: split the keys until the GPU is covered, but keep at least four tiles per CTA
+  long long want = (ctx->sm_count + base_ctas - 1) / base_ctas;
+  want = std::max(1LL, std::min<long long>({want, std::max(1, n_tiles / 4), kDecodeMaxSplits}));
+  const int tiles_per_split = static_cast<int>((n_tiles + want - 1) / want);
+  const int n_splits = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+  CUtensorMap mq, mk, mv;
+  it_status st;
+  const it::TensorStrides sq{D, static_cast<long long>(G) * D, static_cast<long long>(H) * D, Hkv};
+  const it::TensorStrides sc{static_cast<long long>(Hkv) * D, D, static_cast<long long>(max_len) * Hkv * D, Hkv};
+  if ((st = make_tmap(ctx, &mq, q, B, Hkv, G, D, sq, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mk, kc, B, Hkv, kv_len, D, sc, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mv, vc, B, Hkv, kv_len, D, sc, 128)) != IT_OK) return st;
+  auto kernel = it::fa_fwd_pp_sm100_kernel<D, true>;
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    IT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    attr_set[ctx->device & 15] = true;
+  }
+  it::FwdParams p;
+  p.st = it::TensorStrides{D, D, static_cast<long long>(H) * D, H};
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.status = ctx->d_status;
+  p.S = kv_len;
+  p.BH = B * H;
+  p.causal = 0;
+  p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
+  p.kv_group = G;
+  p.dec_tiles_per_split = tiles_per_split;
+  p.dec_n_splits = n_splits;
+  p.dec_part_o = ws;
+  p.dec_part_ml = ws + static_cast<size_t>(B) * H * n_splits * D;
+  kernel<<<static_cast<unsigned>(base_ctas * n_splits), T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  ctx->launches += 1;
+  if (n_splits > 1) {
+    it::fa_decode_merge_kernel<__nv_bfloat16><<<B * H, 128, 0, s>>>(p.dec_part_o, p.dec_part_ml, static_cast<__nv_bfloat16*>(o),
+                                                                    lse, n_splits, D);
+    ctx->launches += 1;
+  }
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
 
 template <typename ST>
 it_status launch_decode(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv, int D, int kv_len, int max_len,
@@ -762,6 +818,9 @@ it_status it_attention_decode(it_ctx* ctx, it_stream* stream, it_dtype dtype, in
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(IT_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
   IT_CUDA(cudaSetDevice(ctx->device));
   float* ws = static_cast<float*>(workspace);
+  if (dtype == IT_BF16 && (D == 64 || D == 128) && H / Hkv <= 128 && kv_len >= 256)
+    return D == 128 ? launch_decode_sm100<128>(ctx, stream->s, B, H, Hkv, kv_len, max_len, q, k_cache, v_cache, o, lse, ws)
+                    : launch_decode_sm100<64>(ctx, stream->s, B, H, Hkv, kv_len, max_len, q, k_cache, v_cache, o, lse, ws);
   return dtype == IT_F32 ? launch_decode<float>(ctx, stream->s, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o, lse, ws)
                          : launch_decode<__nv_bfloat16>(ctx, stream->s, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o,
                                                         lse, ws);
