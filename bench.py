@@ -366,6 +366,34 @@ def run_small(args):
                                                                "unit": "GB/s", "frac": nbytes / med_cold / 1e3 / peaks["hbm"], "traffic": None}}
         print(json.dumps(line), flush=True)
         return
+    if args.workload == "decode":
+        # One new token per sequence against a bf16 key/value cache (grouped heads): the op reads the cache once.
+        B, H, Hkv, D, L = 32, 32, 8, 128, 8192
+        dt = torch.bfloat16
+        q = torch.randn((B, H, D), generator=gen, device="cuda").to(dt)
+        kc = torch.randn((B, L, Hkv, D), generator=gen, device="cuda").to(dt)
+        vc = torch.randn((B, L, Hkv, D), generator=gen, device="cuda").to(dt)
+        o = torch.empty_like(q)
+        lse = torch.empty((B, H), device="cuda")
+        nws = raw.decode_workspace_bytes(B, H, D)
+        ws = torch.empty(nws, dtype=torch.uint8, device="cuda")
+
+        def f():
+            raw.decode(_lib.IT_BF16, B, H, Hkv, D, L, L, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                       ws.data_ptr(), nws, ctx=ctx)
+        for _ in range(max(args.warmup, 3)):
+            f()
+        med, mn = timed(f, args.steps, True)     # the 1.07 GB cache exceeds L2 by itself; flushed anyway
+        nbytes = 2.0 * B * L * Hkv * D * 2 + 2.0 * B * H * D * 2
+        line = {"metric": "KV-cache decode attention, cache bytes per second", "unit": "GB/s", "value": nbytes / med / 1e3,
+                "higher_is_better": True, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bf16",
+                "data": "synthetic", "config": {"workload": "decode B32 H32 kv_heads 8 D128, 8192 cached positions, bf16"},
+                "us": med, "us_min": mn,
+                "roofline": {"bound": "hbm", "achieved": nbytes / med / 1e3, "peak": peaks["hbm"], "unit": "GB/s",
+                             "frac": nbytes / med / 1e3 / peaks["hbm"], "traffic": None,
+                             "note": "peak is the measured copy bandwidth (read + write); a read-only stream can exceed it"}}
+        print(json.dumps(line), flush=True)
+        return
     # c5
     H, D = 4, 64
     lens = list(range(20, 120))
@@ -410,7 +438,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
     ap.add_argument("--slices", type=int, default=0,
@@ -427,7 +455,7 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", port, os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
-    if args.workload in ("c1", "c5"):
+    if args.workload in ("c1", "c5", "decode"):
         if rank == 0:
             run_small(args)
         return

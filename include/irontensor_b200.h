@@ -181,6 +181,18 @@ it_status it_attention_decode(it_ctx* ctx, it_stream* stream, it_dtype dtype, in
                               const void* k_cache, const void* v_cache, void* o, float* lse, void* workspace,
                               size_t workspace_bytes);
 
+/* The projections around attention (src/train/forward.rs:101-103,146; src/train/backward.rs:91,139-147) in bf16:
+ * linear_forward, y = x W^T with x [n, in], W [out, in] (src/train/helpers.rs:48-53: matmul_mps_nt), and
+ * linear_backward, dx = dy W and dW = dy^T x (helpers.rs:61-76: matmul, matmul_mps_tn).  The reference runs
+ * them on MPS in fp32, converting bf16 weights first (ensure_fp32); here x, W, dy, y, dx are bf16, the
+ * accumulation is fp32 in tensor memory, and dW comes back in fp32 as the reference's gradients do.  The
+ * three transposition cases are descriptor bits of one tcgen05 kernel, nothing is transposed in memory.  in and
+ * out must be multiples of 8.  dx or dw may be null (not computed). */
+it_status it_linear_fwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* x,
+                        const void* w, void* y);
+it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* dy,
+                        const void* x, const void* w, void* dx, float* dw);
+
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)
  *

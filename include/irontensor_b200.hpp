@@ -7,6 +7,7 @@
 //   flash_attention              src/ops/flash_attention.rs:76-193     [B,H,S,D]
 //   attention                    src/ops/attention.rs:286-377          [B,S,H,D]
 //   attention_backward_recompute src/train/helpers.rs:120-193          [B,H,S,D]
+//   attention_gqa / rope_qk / attention_decode: the callers' steps around attention folded in (see each)
 // Where the reference panics (assert!), these throw std::logic_error with the same message; failures of
 // the library itself throw it::Error carrying the status code.  Header-only; link libirontensor_b200.so.
 // No CPU fallback: every operation needs the CUDA library and a device.
@@ -18,6 +19,7 @@
 #include <stdexcept>
 #include <string>
 #include <tuple>
+#include <utility>
 #include <vector>
 
 #include "irontensor_b200.h"
@@ -292,6 +294,91 @@ inline std::tuple<Tensor, Tensor, Tensor> attention_backward(const Tensor& grad_
                          static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws.ptr(), ws_bytes));
   CommandBatch::sync();   // the scratch goes out of scope here
   return {dq, dk, dv};
+}
+
+// Grouped-query attention: q [batch, seq, heads, head_dim], k and v [batch, seq, kv_heads, head_dim].  Equal to
+// attention(q, repeat_kv(k), repeat_kv(v), causal) of the reference (src/train/forward.rs:117-139;
+// repeat_kv_gpu, src/ops/repeat_kv.rs:68-149) without the expanded copies.
+inline Tensor attention_gqa(const Tensor& q, const Tensor& k, const Tensor& v, bool causal = true) {
+  require(q.shape().size() == 4 && k.shape().size() == 4 && v.shape().size() == 4, "Q, K and V must be 4D");
+  require(k.shape() == v.shape(), "K and V must have the same shape");
+  const size_t B = q.shape()[0], S = q.shape()[1], H = q.shape()[2], D = q.shape()[3], Hkv = k.shape()[2];
+  require(k.shape()[0] == B && k.shape()[1] == S && k.shape()[3] == D, "K/V must be [batch, seq, kv_heads, head_dim]");
+  require(Hkv >= 1 && H % Hkv == 0, "num_heads must be divisible by num_kv_heads");   // src/ops/repeat_kv.rs:77-80
+  Tensor out = Tensor::zeros({B, S, H, D}, q.precision());
+  out.lse = std::make_shared<Tensor>(Tensor::zeros({B, H, S}, Precision::FP32));
+  if (B * S * H == 0) return out;
+  check(it_attention_gqa_fwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                             static_cast<int32_t>(B), static_cast<int32_t>(S), static_cast<int32_t>(H),
+                             static_cast<int32_t>(Hkv), static_cast<int32_t>(D), causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(),
+                             out.ptr(), static_cast<float*>(out.lse->ptr())));
+  return out;
+}
+
+// (dQ, dK, dV) for attention_gqa(); dK, dV come back summed over each group (repeat_kv_backward,
+// src/ops/repeat_kv.rs:151-232, folded in).  With rope_base > 0, q and k are the ROTATED tensors the
+// forward attended over and dQ, dK are gradients of the un-rotated ones (the reference's two
+// rope_backward passes, src/train/backward.rs:129,132, folded in).
+inline std::tuple<Tensor, Tensor, Tensor> attention_gqa_backward(const Tensor& grad_output, const Tensor& q, const Tensor& k,
+                                                                 const Tensor& v, const Tensor& o, bool causal = true,
+                                                                 float rope_base = 0.f, int position_offset = 0) {
+  const auto& s = q.shape();
+  require(s.size() == 4 && grad_output.shape() == s && o.shape() == s && k.shape() == v.shape(), "shape mismatch");
+  require(static_cast<bool>(o.lse), "o must come from attention_gqa()");
+  const int32_t B = static_cast<int32_t>(s[0]), S = static_cast<int32_t>(s[1]), H = static_cast<int32_t>(s[2]),
+                D = static_cast<int32_t>(s[3]), Hkv = static_cast<int32_t>(k.shape()[2]);
+  Tensor dq = Tensor::zeros(s, q.precision()), dk = Tensor::zeros(k.shape(), q.precision()), dv = Tensor::zeros(k.shape(), q.precision());
+  if (s[0] * s[1] * s[2] == 0) return {dq, dk, dv};
+  size_t ws_bytes = 0;
+  check(it_flash_attention_bwd_workspace_bytes(dtype_code(q.precision()), B, H, S, D, &ws_bytes));
+  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  if (rope_base > 0.f) {
+    check(it_attention_gqa_bwd_rope(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()), B, S, H, Hkv,
+                                    D, causal ? 1 : 0, rope_base, position_offset, q.ptr(), k.ptr(), v.ptr(), o.ptr(),
+                                    grad_output.ptr(), static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(),
+                                    ws.ptr(), ws_bytes));
+  } else {
+    check(it_attention_gqa_bwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()), B, S, H, Hkv, D,
+                               causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), o.ptr(), grad_output.ptr(),
+                               static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws.ptr(), ws_bytes));
+  }
+  CommandBatch::sync();   // the scratch goes out of scope here
+  return {dq, dk, dv};
+}
+
+// rope(q) and rope(k) (src/ops/rope.rs:22-75; src/train/forward.rs:111-112) as one launch; k may have fewer
+// heads.  `inverse` gives the backward rotation.
+inline std::pair<Tensor, Tensor> rope_qk(const Tensor& q, const Tensor& k, float base = 10000.f, int position_offset = 0,
+                                         bool inverse = false) {
+  require(q.shape().size() == 4 && k.shape().size() == 4, "Input must be 4D [batch, seq_len, num_heads, head_dim]");
+  require(q.shape()[3] % 2 == 0, "head_dim must be even for RoPE");
+  require(k.shape()[0] == q.shape()[0] && k.shape()[1] == q.shape()[1] && k.shape()[3] == q.shape()[3], "q and k must agree");
+  Tensor qo = Tensor::empty(q.shape(), q.precision()), ko = Tensor::empty(k.shape(), q.precision());
+  check(it_rope_qk(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                   static_cast<int32_t>(q.shape()[0]), static_cast<int32_t>(q.shape()[1]), static_cast<int32_t>(q.shape()[2]),
+                   static_cast<int32_t>(k.shape()[2]), static_cast<int32_t>(q.shape()[3]), base, position_offset, inverse ? 1 : 0,
+                   q.ptr(), k.ptr(), qo.ptr(), ko.ptr()));
+  return {qo, ko};
+}
+
+// One new token per sequence against a key/value cache: q [batch, heads, head_dim], caches [batch, max_len,
+// kv_heads, head_dim] with the first kv_len positions valid.  (The reference's generator recomputes the whole
+// forward per token, src/inference/generator.rs:146-200.)
+inline Tensor attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, size_t kv_len) {
+  require(q.shape().size() == 3 && k_cache.shape().size() == 4 && k_cache.shape() == v_cache.shape(), "shape mismatch");
+  const int32_t B = static_cast<int32_t>(q.shape()[0]), H = static_cast<int32_t>(q.shape()[1]),
+                D = static_cast<int32_t>(q.shape()[2]), max_len = static_cast<int32_t>(k_cache.shape()[1]),
+                Hkv = static_cast<int32_t>(k_cache.shape()[2]);
+  Tensor out = Tensor::zeros(q.shape(), q.precision());
+  out.lse = std::make_shared<Tensor>(Tensor::zeros({q.shape()[0], q.shape()[1]}, Precision::FP32));
+  size_t ws_bytes = 0;
+  check(it_attention_decode_workspace_bytes(B, H, D, &ws_bytes));
+  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  check(it_attention_decode(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()), B, H, Hkv, D,
+                            static_cast<int32_t>(kv_len), max_len, q.ptr(), k_cache.ptr(), v_cache.ptr(), out.ptr(),
+                            static_cast<float*>(out.lse->ptr()), ws.ptr(), ws_bytes));
+  CommandBatch::sync();
+  return out;
 }
 
 }  // namespace it

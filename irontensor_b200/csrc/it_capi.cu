@@ -23,6 +23,7 @@
 #include "fa_fwd_sm100.cuh"
 #include "fa_decode.cuh"
 #include "fa_fwd_pp_sm100.cuh"
+#include "gemm_sm100.cuh"
 #include "fa_generic.cuh"
 #include "selftest_sm100.cuh"
 
@@ -323,6 +324,48 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
 }
 
 constexpr int kDecodeMaxSplits = 64;
+
+// C[M,N] = op(A) op(B) in bf16 with fp32 accumulation.  layout 0: A [M,K], B [N,K]; 1: A [M,K], B [K,N];
+// 2: A [K,M], B [K,N].  Row-major, pitches in elements.
+template <int LAYOUT>
+it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const void* a, long long lda, const void* b,
+                      long long ldb, void* c, long long ldc, bool c_is_f32) {
+  using T = it::GemmTraits;
+  CUtensorMap ma, mb;
+  it_status st;
+  const int a_rows = (LAYOUT == 2) ? K : M, a_cols = (LAYOUT == 2) ? M : K;
+  const int b_rows = (LAYOUT == 0) ? N : K, b_cols = (LAYOUT == 0) ? K : N;
+  const it::TensorStrides sa{lda, lda * a_rows, lda * a_rows, 1}, sb{ldb, ldb * b_rows, ldb * b_rows, 1};
+  if ((st = make_tmap(ctx, &ma, a, 1, 1, a_rows, a_cols, sa, (LAYOUT == 2) ? T::BK : T::BM)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mb, b, 1, 1, b_rows, b_cols, sb, (LAYOUT == 0) ? T::BN : T::BK)) != IT_OK) return st;
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    IT_CUDA(cudaFuncSetAttribute(it::gemm_bf16_sm100_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    attr_set[ctx->device & 15] = true;
+  }
+  it::GemmParams p;
+  p.c = c;
+  p.ldc = ldc;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.c_is_f32 = c_is_f32 ? 1 : 0;
+  p.status = ctx->d_status;
+  const int n_tiles = ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
+  const int grid = std::min(n_tiles, ctx->sm_count);
+  it::gemm_bf16_sm100_kernel<LAYOUT><<<grid, T::THREADS, T::SMEM_BYTES, s>>>(ma, mb, p);
+  ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
+}
+
+it_status check_linear(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (n < 0 || in_dim < 0 || out_dim < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  if ((in_dim & 7) || (out_dim & 7))
+    return fail(IT_ERR_UNSUPPORTED_SHAPE, "in and out dimensions must be multiples of 8, got %d and %d", in_dim, out_dim);
+  return IT_OK;
+}
 
 // Decode on the tensor-core pipeline (bf16, head_dim 64 or 128): the group's query heads are the rows of
 // one query tile, the cache is streamed by TMA.  See fa_fwd_pp_sm100.cuh, DECODE.
@@ -824,6 +867,44 @@ it_status it_attention_decode(it_ctx* ctx, it_stream* stream, it_dtype dtype, in
   return dtype == IT_F32 ? launch_decode<float>(ctx, stream->s, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o, lse, ws)
                          : launch_decode<__nv_bfloat16>(ctx, stream->s, B, H, Hkv, D, kv_len, max_len, q, k_cache, v_cache, o,
                                                         lse, ws);
+}
+
+it_status it_linear_fwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* x,
+                        const void* w, void* y) {
+  it_status st = check_linear(ctx, stream, n, in_dim, out_dim);
+  if (st != IT_OK) return st;
+  if (n == 0 || out_dim == 0) return IT_OK;
+  if (x == nullptr || w == nullptr || y == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y)) return fail(IT_ERR_ALIGNMENT, "x, w and y must be 16-byte aligned");
+  if (in_dim == 0) {
+    IT_CUDA(cudaMemsetAsync(y, 0, static_cast<size_t>(n) * out_dim * 2, stream->s));
+    return IT_OK;
+  }
+  IT_CUDA(cudaSetDevice(ctx->device));
+  return launch_gemm<0>(ctx, stream->s, n, out_dim, in_dim, x, in_dim, w, in_dim, y, out_dim, false);
+}
+
+it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* dy,
+                        const void* x, const void* w, void* dx, float* dw) {
+  it_status st = check_linear(ctx, stream, n, in_dim, out_dim);
+  if (st != IT_OK) return st;
+  if (in_dim == 0 || (n == 0 && out_dim == 0)) return IT_OK;
+  if (dy == nullptr || x == nullptr || w == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || (dx && !aligned16(dx)) || (dw && !aligned16(dw)))
+    return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  if (n == 0 || out_dim == 0) {   // empty sums
+    if (dx && n) IT_CUDA(cudaMemsetAsync(dx, 0, static_cast<size_t>(n) * in_dim * 2, stream->s));
+    if (dw && out_dim) IT_CUDA(cudaMemsetAsync(dw, 0, static_cast<size_t>(out_dim) * in_dim * 4, stream->s));
+    return IT_OK;
+  }
+  if (dx != nullptr &&
+      (st = launch_gemm<1>(ctx, stream->s, n, in_dim, out_dim, dy, out_dim, w, in_dim, dx, in_dim, false)) != IT_OK)
+    return st;
+  if (dw != nullptr &&
+      (st = launch_gemm<2>(ctx, stream->s, out_dim, in_dim, n, dy, out_dim, x, in_dim, dw, in_dim, true)) != IT_OK)
+    return st;
+  return IT_OK;
 }
 
 // Scratch for it_flash_attention_bwd_noalloc: part of the module image on every GPU that loads it.

@@ -333,6 +333,16 @@ class raw:
                                              v_cache, o, lse, ws, ws_bytes))
 
     @staticmethod
+    def linear_fwd(n, in_dim, out_dim, x, w, y, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_linear_fwd(c.handle, c.stream(), n, in_dim, out_dim, x, w, y))
+
+    @staticmethod
+    def linear_bwd(n, in_dim, out_dim, dy, x, w, dx, dw, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_linear_bwd(c.handle, c.stream(), n, in_dim, out_dim, dy, x, w, dx, dw))
+
+    @staticmethod
     def bwd_workspace_bytes(dtype, B, H, S, D):
         n = ctypes.c_size_t()
         _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))
@@ -528,6 +538,29 @@ def attention_decode(q, k_cache, v_cache, kv_len):
     raw.decode(_dtype_code(p), B, H, Hkv, D, kv_len, max_len, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                out.data_ptr(), out.lse.data_ptr(), ws.data_ptr(), ws.numel())
     return out
+
+
+def linear_forward(input, weight):
+    """output = input @ weight.T (src/train/helpers.rs:48-53) for BF16 tensors: input [n, in], weight [out, in]."""
+    assert input.precision() is Precision.BF16 and weight.precision() is Precision.BF16, "linear_forward takes BF16 tensors"
+    n, k = input.shape()
+    out_dim, k2 = weight.shape()
+    assert k == k2, "inner dimensions must match"
+    y = Tensor.empty([n, out_dim], Precision.BF16)
+    raw.linear_fwd(n, k, out_dim, input.data_ptr(), weight.data_ptr(), y.data_ptr())
+    return y
+
+
+def linear_backward(grad_output, input, weight):
+    """(grad_input, grad_weight) = (grad_output @ weight, grad_output.T @ input) (src/train/helpers.rs:61-76);
+    grad_input BF16 [n, in], grad_weight FP32 [out, in] (the reference returns FP32 gradients)."""
+    n, out_dim = grad_output.shape()
+    k = input.shape()[1]
+    assert input.shape() == [n, k] and weight.shape() == [out_dim, k]
+    dx = Tensor.empty([n, k], Precision.BF16)
+    dw = Tensor.empty([out_dim, k], Precision.FP32)
+    raw.linear_bwd(n, k, out_dim, grad_output.data_ptr(), input.data_ptr(), weight.data_ptr(), dx.data_ptr(), dw.data_ptr())
+    return dx, dw
 
 
 def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=True):

@@ -191,6 +191,48 @@ int main() {
       EXPECT(max_abs_diff(sdv.to_host_f32(), to_bshd(dv.to_host_f32())) == 0.0, "[B,S,H,D] dV equals [B,H,S,D] dV");
       EXPECT(max_abs_diff(sdq.to_host_f32(), to_bshd(ref.dq)) < 2e-2, "[B,S,H,D] dQ");
     }
+    // --- grouped queries, rotary embedding, key/value cache: against the plain ops on expanded / full tensors
+    {
+      const size_t B = 1, S = 48, H = 4, Hkv = 2, D = 16;
+      std::vector<float> q(B * S * H * D), k(B * S * Hkv * D), v(k.size()), go(q.size());
+      for (size_t i = 0; i < q.size(); ++i) { q[i] = std::sin(0.37f * i); go[i] = std::cos(0.23f * i); }
+      for (size_t i = 0; i < k.size(); ++i) { k[i] = std::cos(0.11f * i); v[i] = std::sin(0.05f * i + 1.f); }
+      auto expand = [&](const std::vector<float>& x) {   // repeat_kv: [B,S,Hkv,D] -> [B,S,H,D]
+        std::vector<float> y(B * S * H * D);
+        for (size_t bs = 0; bs < B * S; ++bs) for (size_t h = 0; h < H; ++h) for (size_t d = 0; d < D; ++d)
+          y[(bs * H + h) * D + d] = x[(bs * Hkv + h / (H / Hkv)) * D + d];
+        return y;
+      };
+      const Tensor tq = Tensor::from_f32_slice(q, {B, S, H, D}), tk = Tensor::from_f32_slice(k, {B, S, Hkv, D}),
+                   tv = Tensor::from_f32_slice(v, {B, S, Hkv, D}), tgo = Tensor::from_f32_slice(go, {B, S, H, D});
+      const Tensor o = it::attention_gqa(tq, tk, tv, true);
+      const Tensor ke = Tensor::from_f32_slice(expand(k), {B, S, H, D}), ve = Tensor::from_f32_slice(expand(v), {B, S, H, D});
+      const Tensor oe = it::attention(tq, ke, ve, true);
+      EXPECT(max_abs_diff(o.to_host_f32(), oe.to_host_f32()) < 1e-6, "attention_gqa equals attention on expanded K/V");
+      auto [dq, dk, dv] = it::attention_gqa_backward(tgo, tq, tk, tv, o, true);
+      auto [dqe, dke, dve] = it::attention_backward(tgo, tq, ke, ve, oe, true);
+      EXPECT(max_abs_diff(dq.to_host_f32(), dqe.to_host_f32()) < 1e-5, "grouped dQ");
+      std::vector<float> fold(B * S * Hkv * D, 0.f);   // repeat_kv_backward
+      const std::vector<float> dkeh = dke.to_host_f32();
+      for (size_t bs = 0; bs < B * S; ++bs) for (size_t h = 0; h < H; ++h) for (size_t d = 0; d < D; ++d)
+        fold[(bs * Hkv + h / (H / Hkv)) * D + d] += dkeh[(bs * H + h) * D + d];
+      EXPECT(max_abs_diff(dk.to_host_f32(), fold) < 1e-5, "grouped dK is the sum over the group");
+      // rotary: position 0 is the identity, inverse(forward) is the identity
+      auto [qr, kr] = it::rope_qk(tq, tk);
+      const std::vector<float> qrh = qr.to_host_f32();
+      double m0 = 0;
+      for (size_t i = 0; i < H * D; ++i) m0 = std::max(m0, std::fabs(static_cast<double>(qrh[i]) - q[i]));
+      EXPECT(m0 == 0.0, "rope at position 0 is the identity");
+      auto [qb, kb] = it::rope_qk(qr, kr, 10000.f, 0, true);
+      EXPECT(max_abs_diff(qb.to_host_f32(), q) < 1e-5 && max_abs_diff(kb.to_host_f32(), k) < 1e-5, "rope inverse");
+      // key/value cache: the new token's output equals the last row of the full causal attention
+      std::vector<float> q_last(H * D);
+      for (size_t i = 0; i < H * D; ++i) q_last[i] = q[((S - 1) * H) * D + i];
+      const Tensor dec = it::attention_decode(Tensor::from_f32_slice(q_last, {B, H, D}), tk, tv, S);
+      const std::vector<float> oh = o.to_host_f32();
+      std::vector<float> want(oh.begin() + (S - 1) * H * D, oh.begin() + S * H * D);
+      EXPECT(max_abs_diff(dec.to_host_f32(), want) < 1e-5, "decode equals the last row");
+    }
     // --- the reference's asserts
     {
       const Tensor a = Tensor::zeros({2, 4, 32, 16}), b = Tensor::zeros({2, 4, 33, 16});

@@ -555,3 +555,25 @@ def test_kv_cache_decode_over_a_generation(it_ctx):
         worst = max(worst, float(np.abs(got.to_f32_host() - want).max()))
     assert it_ctx.poll_status() == 0
     assert worst <= F32_TOL, worst
+
+
+@pytest.mark.parametrize("n,k,out", [(128, 64, 256), (300, 200, 264), (1000, 1024, 768), (130, 72, 40), (4096, 2048, 512), (64, 8, 8)])
+def test_projection_gemms_match_fp32_matmul(it_ctx, n, k, out):
+    """linear_forward / linear_backward (src/train/helpers.rs:48-76) on the tcgen05 GEMM, the three transposition
+    cases, against fp32 matmuls of the same bf16-rounded operands (what the reference computes after ensure_fp32).
+    Sizes cover edge tiles in M, N and K."""
+    from irontensor_b200 import Tensor, linear_backward, linear_forward
+    x = synth.round_bf16(synth.normal(170, synth.TENSOR_Q, 0, n * k, 1.0)).reshape(n, k)
+    w = synth.round_bf16(synth.normal(170, synth.TENSOR_K, 0, out * k, 0.05)).reshape(out, k)
+    dy = synth.round_bf16(synth.normal(170, synth.TENSOR_DO, 0, n * out, 1.0)).reshape(n, out)
+    tx, tw, tdy = (Tensor.from_f32_as_bf16(a.reshape(-1), list(a.shape)) for a in (x, w, dy))
+    y = linear_forward(tx, tw).to_f32_host()
+    dx, dw = linear_backward(tdy, tx, tw)
+    assert it_ctx.poll_status() == 0
+    x64, w64, dy64 = x.astype(np.float64), w.astype(np.float64), dy.astype(np.float64)
+    for got, want, name, exact_store in ((y, x64 @ w64.T, "y", False), (dx.to_f32_host(), dy64 @ w64, "dx", False),
+                                         (dw.to_f32_host(), dy64.T @ x64, "dW", True)):
+        err = np.abs(got - want).max()
+        scale = np.abs(want).max() + 1e-30
+        # bf16 results carry half an ulp (2^-9 relative) of storage rounding; the fp32 dW only accumulation error
+        assert err <= (2e-5 if exact_store else 4.5e-3) * scale, f"{name} n={n} k={k} out={out}: {err} vs scale {scale}"
