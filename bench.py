@@ -394,6 +394,40 @@ def run_small(args):
                              "note": "peak is the measured copy bandwidth (read + write); a read-only stream can exceed it"}}
         print(json.dumps(line), flush=True)
         return
+    if args.workload == "linear":
+        # The projections around attention for the C4 token count: n = B*S = 32768 tokens, hidden 2048,
+        # fused QKV width (16 + 2*16 heads of 128) = 6144: y = x W^T, dx = dy W, dW = dy^T x.
+        n, k, out = 32768, 2048, 6144
+        x = torch.randn((n, k), generator=gen, device="cuda").to(torch.bfloat16)
+        w = (torch.randn((out, k), generator=gen, device="cuda") * 0.05).to(torch.bfloat16)
+        dy = torch.randn((n, out), generator=gen, device="cuda").to(torch.bfloat16)
+        y = torch.empty((n, out), dtype=torch.bfloat16, device="cuda")
+        dx = torch.empty_like(x)
+        dw = torch.empty((out, k), device="cuda")
+
+        def f():
+            raw.linear_fwd(n, k, out, x.data_ptr(), w.data_ptr(), y.data_ptr(), ctx=ctx)
+            raw.linear_bwd(n, k, out, dy.data_ptr(), x.data_ptr(), w.data_ptr(), dx.data_ptr(), dw.data_ptr(), ctx=ctx)
+
+        def lib():   # the same three products through torch (cuBLAS), for the ratio only
+            torch.matmul(x, w.t())
+            torch.matmul(dy, w)
+            torch.matmul(dy.t(), x)
+        for _ in range(max(args.warmup, 3)):
+            f()
+            lib()
+        med, mn = timed(f, args.steps, True)
+        med_lib, _ = timed(lib, args.steps, True)
+        flops = 3 * 2.0 * n * k * out
+        line = {"metric": "projection GEMMs fwd+bwd TFLOP/s", "unit": "TFLOP/s", "value": flops / med / 1e6,
+                "higher_is_better": True, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bf16",
+                "data": "synthetic", "config": {"workload": "linear forward + backward, 32768 tokens, 2048 -> 6144, bf16"},
+                "us": med, "us_min": mn, "gpu_launches": 3 * (args.steps + max(args.warmup, 3)),
+                "cublas_same_box_tflops": flops / med_lib / 1e6,
+                "roofline": {"bound": "tensor", "achieved": flops / med / 1e6, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                             "frac": flops / med / 1e6 / peaks["bf16"], "traffic": None}}
+        print(json.dumps(line), flush=True)
+        return
     # c5
     H, D = 4, 64
     lens = list(range(20, 120))
@@ -438,7 +472,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode", "linear"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
     ap.add_argument("--slices", type=int, default=0,
@@ -455,7 +489,7 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", port, os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
-    if args.workload in ("c1", "c5", "decode"):
+    if args.workload in ("c1", "c5", "decode", "linear"):
         if rank == 0:
             run_small(args)
         return

@@ -13,3 +13,35 @@ def shard_range(n_slices, world_size, rank):
     per = -(-n_slices // world_size)
     begin = min(n_slices, rank * per)
     return begin, min(n_slices, begin + per)
+
+
+# ---------------------------------------------------------------- head-parallel projections
+# With the heads of a layer split over the GPUs (each rank owns heads [h0, h1) and the K/V heads they read),
+# the Q/K/V projections need only the rank's rows of Wq, Wk, Wv (src/train/forward.rs:101-103: out = heads *
+# head_dim rows per weight), attention runs on the rank's heads with no exchange, and the output projection
+# (forward.rs:146: attn [n, heads*head_dim] @ Wo.T) becomes a sum over ranks of partial products over each
+# rank's COLUMNS of Wo: the one real exchange step on the path, an all-reduce of [n, hidden].
+
+def head_shard(num_heads, num_kv_heads, world_size, rank):
+    """(q_head_begin, q_head_end, kv_head_begin, kv_head_end) for `rank`: whole K/V groups, contiguous, so that every
+    query head finds its K/V head on the same rank."""
+    if num_heads % num_kv_heads:
+        raise ValueError("num_heads must be divisible by num_kv_heads")
+    group = num_heads // num_kv_heads
+    kb, ke = shard_range(num_kv_heads, world_size, rank)
+    return kb * group, ke * group, kb, ke
+
+
+def qkv_weight_rows(num_heads, num_kv_heads, head_dim, world_size, rank):
+    """Row ranges [begin, end) of Wq, Wk and Wv ([heads*head_dim, hidden] each) that `rank` multiplies by."""
+    qb, qe, kb, ke = head_shard(num_heads, num_kv_heads, world_size, rank)
+    return (qb * head_dim, qe * head_dim), (kb * head_dim, ke * head_dim), (kb * head_dim, ke * head_dim)
+
+
+def out_projection_all_reduce(partial, group=None):
+    """Sums the ranks' partial output projections in place (NCCL on GPUs, gloo in the CPU tests) and returns it.
+    `partial` is this rank's attn[:, its heads] @ Wo[:, its columns].T, a torch tensor [n, hidden]."""
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
+    return partial

@@ -105,3 +105,65 @@ def test_two_rank_max_reduction_over_gloo(tmp_path):
                          capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "OK 15.0" in out.stdout
+
+
+def test_head_shards_keep_groups_together():
+    from irontensor_b200.sharding import head_shard, qkv_weight_rows
+    for H, Hkv, W in ((16, 16, 4), (32, 8, 8), (12, 4, 3), (8, 2, 4), (6, 3, 2)):
+        seen_q, seen_kv = [], []
+        for r in range(W):
+            qb, qe, kb, ke = head_shard(H, Hkv, W, r)
+            assert (qe - qb) == (ke - kb) * (H // Hkv)
+            for h in range(qb, qe):
+                assert kb <= h // (H // Hkv) < ke          # the K/V head a query head reads is on the same rank
+            seen_q += list(range(qb, qe))
+            seen_kv += list(range(kb, ke))
+            (q0, q1), (k0, k1), (v0, v1) = qkv_weight_rows(H, Hkv, 64, W, r)
+            assert (q0, q1, k0, k1) == (qb * 64, qe * 64, kb * 64, ke * 64) and (v0, v1) == (k0, k1)
+        assert seen_q == list(range(H)) and seen_kv == list(range(Hkv))
+    with pytest.raises(ValueError):
+        head_shard(10, 4, 2, 0)
+
+
+def test_head_parallel_projections_sum_to_the_full_layer_over_gloo(tmp_path):
+    """Two ranks, heads split between them: each projects with its rows of Wq/Wk/Wv, attends over its heads, multiplies by
+    its columns of Wo, and the all-reduce of the partial outputs equals the unsharded layer (fp64 on CPU; the GPU
+    kernels are exercised by the gpu tests, this covers the sharding arithmetic and the one collective)."""
+    script = tmp_path / "tp.py"
+    script.write_text(textwrap.dedent(f"""
+        import sys
+        sys.path.insert(0, {ROOT!r})
+        import numpy as np, torch, torch.distributed as dist
+        from irontensor_b200.sharding import head_shard, qkv_weight_rows, out_projection_all_reduce
+        dist.init_process_group("gloo")
+        r, w = dist.get_rank(), dist.get_world_size()
+        S, hidden, H, Hkv, D = 12, 32, 4, 2, 8
+        rng = np.random.default_rng(3)                      # same data on every rank
+        x = rng.standard_normal((S, hidden)); wq = rng.standard_normal((H * D, hidden)); wk = rng.standard_normal((Hkv * D, hidden))
+        wv = rng.standard_normal((Hkv * D, hidden)); wo = rng.standard_normal((hidden, H * D))
+        def attend(q, k, v):                                # q [S,h,D], k/v [S,hk,D], causal, grouped
+            g = q.shape[1] // k.shape[1]
+            out = np.zeros_like(q)
+            for h in range(q.shape[1]):
+                s = q[:, h] @ k[:, h // g].T / np.sqrt(D)
+                s = np.where(np.tril(np.ones((S, S), bool)), s, -np.inf)
+                p = np.exp(s - s.max(1, keepdims=True)); p /= p.sum(1, keepdims=True)
+                out[:, h] = p @ v[:, h // g]
+            return out
+        full = attend((x @ wq.T).reshape(S, H, D), (x @ wk.T).reshape(S, Hkv, D), (x @ wv.T).reshape(S, Hkv, D)).reshape(S, H * D) @ wo.T
+        (q0, q1), (k0, k1), (v0, v1) = qkv_weight_rows(H, Hkv, D, w, r)
+        qb, qe, kb, ke = head_shard(H, Hkv, w, r)
+        mine = attend((x @ wq[q0:q1].T).reshape(S, qe - qb, D), (x @ wk[k0:k1].T).reshape(S, ke - kb, D),
+                      (x @ wv[v0:v1].T).reshape(S, ke - kb, D)).reshape(S, (qe - qb) * D)
+        partial = torch.from_numpy(mine @ wo[:, q0:q1].T)
+        total = out_projection_all_reduce(partial)
+        assert np.abs(total.numpy() - full).max() < 1e-10
+        dist.barrier()
+        if r == 0: print("OK")
+        dist.destroy_process_group()
+    """))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                         capture_output=True, text=True, timeout=240)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "OK" in out.stdout
