@@ -193,6 +193,19 @@ it_status it_linear_fwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_di
 it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* dy,
                         const void* x, const void* w, void* dx, float* dw);
 
+/* The Q, K and V projections and the rotary embedding of Q and K as ONE kernel: x [batch*seq, hidden] times the
+ * stacked weights w_qkv = [Wq; Wk; Wv] ([(heads + 2*kv_heads)*head_dim, hidden]), the rotation applied in the
+ * GEMM's epilogue, q_out [batch, seq, heads, head_dim], k_out and v_out [batch, seq, kv_heads, head_dim] written
+ * in the layout it_attention_gqa_* read.  The reference runs three linear_forward calls on the same input and
+ * rope() twice (src/train/forward.rs:101-103,111-112).  rope_base 0 leaves Q and K un-rotated.  bf16; head_dim
+ * 32, 64, 96 or 128; hidden a multiple of 8.  workspace (it_qkv_rope_workspace_bytes, 256-byte aligned; may be
+ * null when rope_base is 0) holds the cosine/sine table of the call. */
+it_status it_qkv_rope_workspace_bytes(int32_t seq, int32_t head_dim, size_t* out_bytes);
+it_status it_qkv_rope_fwd(it_ctx* ctx, it_stream* stream, int32_t batch, int32_t seq, int32_t hidden, int32_t heads,
+                          int32_t kv_heads, int32_t head_dim, float rope_base, int32_t position_offset, const void* x,
+                          const void* w_qkv, void* q_out, void* k_out, void* v_out, void* workspace,
+                          size_t workspace_bytes);
+
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)
  *

@@ -55,6 +55,8 @@ SIGNATURES = {
     "it_attention_decode_workspace_bytes": [_i32, _i32, _i32, _c.POINTER(_c.c_size_t)],
     "it_attention_decode": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_size_t],
     "it_linear_fwd": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp],
+    "it_qkv_rope_workspace_bytes": [_i32, _i32, _c.POINTER(_c.c_size_t)],
+    "it_qkv_rope_fwd": [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _c.c_float, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_size_t],
     "it_linear_bwd": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "it_flash_attention_bwd_noalloc": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9,
     "it_attention_status_poll": [_vp, _vp, _c.POINTER(_i32)],

@@ -18,6 +18,7 @@
 // K and the row pitches must be multiples of 8 elements (16-byte rows for TMA); M, N, K are
 // otherwise free (edges are zero-filled on load and masked on store).
 #pragma once
+#include "rope.cuh"
 #include "sm100_ptx.cuh"
 
 namespace it {
@@ -41,6 +42,12 @@ struct GemmParams {
   int M, N, K;
   int c_is_f32;
   int* status;
+  // QKV epilogue (gemm_bf16_sm100_kernel<0, true>): the N columns are [heads*D of Q | kv_heads*D of K | kv_heads*D
+  // of V]; row r is token (batch, r % seq).  Q and K columns are rotated by the token's position and the three
+  // ranges are stored to q [M, heads, D], k and v [M, kv_heads, D].
+  __nv_bfloat16 *q, *k, *v;
+  int seq, heads, kv_heads, head_dim;
+  const float2* rope_table;   // [seq][head_dim / 2] (cos, sin), or null: no rotation
 };
 
 // Tile index -> tile coordinates.  Tiles are numbered in groups of 16 rows of tiles: within a group the M
@@ -59,7 +66,12 @@ __device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tile
   *tn = in_group / gm;
 }
 
-template <int LAYOUT>
+// QKV = true (layout 0 only) is the fused Q/K/V projection: one GEMM over the stacked weights
+// [Wq; Wk; Wv] (the reference runs three linear_forward calls on the same input and then rope() twice:
+// src/train/forward.rs:101-103,111-112) whose epilogue applies the rotary embedding to the Q and K
+// columns - a rotation pair is two neighbouring accumulator registers of the thread that owns the token's
+// row; cosines and sines come from a table built once per call - and writes q_rope, k_rope and v in the [batch, seq, heads, head_dim] layout attention reads.
+template <int LAYOUT, bool QKV = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmParams prm) {
@@ -194,7 +206,51 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         tmem_ld_x32(t_lane + buf * T::BN + c * 32, r);
         tmem_wait_ld();
         const int col = n0 + c * 32;
-        if (row < prm.M && col < prm.N) {
+        if (QKV) {
+          if (row < prm.M && col < prm.N) {   // head_dim is a multiple of 32: a chunk lies inside one head of one tensor
+            const int hd_total = prm.heads * prm.head_dim, kv_total = prm.kv_heads * prm.head_dim;
+            __nv_bfloat16* dst;
+            int d0;
+            bool rotate = true;
+            if (col < hd_total) {
+              d0 = col % prm.head_dim;
+              dst = prm.q + (static_cast<long long>(row) * prm.heads + col / prm.head_dim) * prm.head_dim + d0;
+            } else if (col < hd_total + kv_total) {
+              const int cc = col - hd_total;
+              d0 = cc % prm.head_dim;
+              dst = prm.k + (static_cast<long long>(row) * prm.kv_heads + cc / prm.head_dim) * prm.head_dim + d0;
+            } else {
+              const int cc = col - hd_total - kv_total;
+              d0 = cc % prm.head_dim;
+              dst = prm.v + (static_cast<long long>(row) * prm.kv_heads + cc / prm.head_dim) * prm.head_dim + d0;
+              rotate = false;
+            }
+            if (rotate && prm.rope_table != nullptr) {
+              // 16 (cos, sin) pairs of this token's position: 128 contiguous bytes of the table
+              const float4* tab = reinterpret_cast<const float4*>(prm.rope_table + static_cast<size_t>(row % prm.seq) * (prm.head_dim >> 1) +
+                                                                  (d0 >> 1));
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 cs = __ldg(tab + i);   // (cos, sin) of pairs 2i and 2i+1
+                const float a0 = __uint_as_float(r[4 * i]), a1 = __uint_as_float(r[4 * i + 1]);
+                const float b0 = __uint_as_float(r[4 * i + 2]), b1 = __uint_as_float(r[4 * i + 3]);
+                r[4 * i] = __float_as_uint(a0 * cs.x - a1 * cs.y);
+                r[4 * i + 1] = __float_as_uint(a0 * cs.y + a1 * cs.x);
+                r[4 * i + 2] = __float_as_uint(b0 * cs.z - b1 * cs.w);
+                r[4 * i + 3] = __float_as_uint(b0 * cs.w + b1 * cs.z);
+              }
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              w.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              w.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              w.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + v * 8) = w;
+            }
+          }
+        } else if (row < prm.M && col < prm.N) {
           if (prm.c_is_f32) {
             float* dst = static_cast<float*>(prm.c) + static_cast<long long>(row) * prm.ldc + col;
             if (col + 32 <= prm.N && (prm.ldc & 3) == 0) {

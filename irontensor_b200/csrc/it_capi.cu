@@ -327,9 +327,15 @@ constexpr int kDecodeMaxSplits = 64;
 
 // C[M,N] = op(A) op(B) in bf16 with fp32 accumulation.  layout 0: A [M,K], B [N,K]; 1: A [M,K], B [K,N];
 // 2: A [K,M], B [K,N].  Row-major, pitches in elements.
-template <int LAYOUT>
+struct QkvEpilogue {
+  void *q, *k, *v;
+  int seq, heads, kv_heads, head_dim;
+  const float2* rope_table;
+};
+
+template <int LAYOUT, bool QKV = false>
 it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const void* a, long long lda, const void* b,
-                      long long ldb, void* c, long long ldc, bool c_is_f32) {
+                      long long ldb, void* c, long long ldc, bool c_is_f32, const QkvEpilogue* epi = nullptr) {
   using T = it::GemmTraits;
   CUtensorMap ma, mb;
   it_status st;
@@ -340,7 +346,8 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   if ((st = make_tmap(ctx, &mb, b, 1, 1, b_rows, b_cols, sb, (LAYOUT == 0) ? T::BN : T::BK)) != IT_OK) return st;
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    IT_CUDA(cudaFuncSetAttribute(it::gemm_bf16_sm100_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    IT_CUDA(cudaFuncSetAttribute(it::gemm_bf16_sm100_kernel<LAYOUT, QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
   }
   it::GemmParams p;
@@ -351,9 +358,22 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   p.K = K;
   p.c_is_f32 = c_is_f32 ? 1 : 0;
   p.status = ctx->d_status;
+  p.q = p.k = p.v = nullptr;
+  p.seq = p.heads = p.kv_heads = p.head_dim = 0;
+  p.rope_table = nullptr;
+  if (epi != nullptr) {
+    p.q = static_cast<__nv_bfloat16*>(epi->q);
+    p.k = static_cast<__nv_bfloat16*>(epi->k);
+    p.v = static_cast<__nv_bfloat16*>(epi->v);
+    p.seq = epi->seq;
+    p.heads = epi->heads;
+    p.kv_heads = epi->kv_heads;
+    p.head_dim = epi->head_dim;
+    p.rope_table = epi->rope_table;
+  }
   const int n_tiles = ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
   const int grid = std::min(n_tiles, ctx->sm_count);
-  it::gemm_bf16_sm100_kernel<LAYOUT><<<grid, T::THREADS, T::SMEM_BYTES, s>>>(ma, mb, p);
+  it::gemm_bf16_sm100_kernel<LAYOUT, QKV><<<grid, T::THREADS, T::SMEM_BYTES, s>>>(ma, mb, p);
   ctx->launches += 1;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -882,6 +902,51 @@ it_status it_linear_fwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_di
   }
   IT_CUDA(cudaSetDevice(ctx->device));
   return launch_gemm<0>(ctx, stream->s, n, out_dim, in_dim, x, in_dim, w, in_dim, y, out_dim, false);
+}
+
+it_status it_qkv_rope_workspace_bytes(int32_t S, int32_t D, size_t* out_bytes) {
+  if (out_bytes == nullptr) return fail(IT_ERR_INVALID_ARG, "out_bytes is null");
+  if (S < 0 || D < 2 || D > 128 || (D & 1)) return fail(IT_ERR_INVALID_ARG, "bad seq or head_dim");
+  *out_bytes = (static_cast<size_t>(S) * (D / 2) * sizeof(float2) + 255) / 256 * 256 + 256;
+  return IT_OK;
+}
+
+it_status it_qkv_rope_fwd(it_ctx* ctx, it_stream* stream, int32_t B, int32_t S, int32_t hidden, int32_t H, int32_t Hkv,
+                          int32_t D, float rope_base, int32_t position_offset, const void* x, const void* w_qkv,
+                          void* q_out, void* k_out, void* v_out, void* workspace, size_t workspace_bytes) {
+  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null context or stream");
+  if (B < 0 || S < 0 || hidden < 1 || H < 1) return fail(IT_ERR_INVALID_ARG, "bad dimension");
+  it_status st = check_kv_heads(H, Hkv);
+  if (st != IT_OK) return st;
+  if (D != 32 && D != 64 && D != 96 && D != 128)
+    return fail(IT_ERR_UNSUPPORTED_SHAPE, "head_dim must be 32, 64, 96 or 128 for the fused projection, got %d", D);
+  if (hidden & 7) return fail(IT_ERR_UNSUPPORTED_SHAPE, "hidden must be a multiple of 8, got %d", hidden);
+  if (rope_base != 0.f && (st = check_rope(D, rope_base)) != IT_OK) return st;
+  const long long n = static_cast<long long>(B) * S;
+  if (n == 0) return IT_OK;
+  if (n > 0x7fffffffLL) return fail(IT_ERR_UNSUPPORTED_SHAPE, "too many tokens");
+  if (x == nullptr || w_qkv == nullptr || q_out == nullptr || k_out == nullptr || v_out == nullptr)
+    return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(x) || !aligned16(w_qkv) || !aligned16(q_out) || !aligned16(k_out) || !aligned16(v_out))
+    return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  const float2* table = nullptr;
+  if (rope_base != 0.f) {
+    size_t need = 0;
+    it_qkv_rope_workspace_bytes(S, D, &need);
+    if (workspace == nullptr || workspace_bytes < need)
+      return fail(IT_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(IT_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    const int cells = S * (D / 2);
+    it::rope_table_kernel<<<(cells + 255) / 256, 256, 0, stream->s>>>(static_cast<float2*>(workspace), S, D / 2,
+                                                                      make_rope_freqs(D, rope_base, position_offset, true));
+    ctx->launches += 1;
+    table = static_cast<const float2*>(workspace);
+  }
+  QkvEpilogue epi{q_out, k_out, v_out, S, H, Hkv, D, table};
+  const int out_dim = (H + 2 * Hkv) * D;
+  return launch_gemm<0, true>(ctx, stream->s, static_cast<int>(n), out_dim, hidden, x, hidden, w_qkv, hidden, nullptr, 0,
+                              false, &epi);
 }
 
 it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* dy,

@@ -65,4 +65,14 @@ rope_qk_kernel(const ST* __restrict__ q_in, const ST* __restrict__ k_in, ST* __r
   }
 }
 
+// (cos, sin) of every (sequence index, dimension pair): [S][D/2] float2.  Built once per call by kernels
+// that would otherwise evaluate the same sine and cosine in every column tile (the fused QKV projection).
+__global__ void rope_table_kernel(float2* __restrict__ table, int S, int half, const __grid_constant__ RopeFreqs freqs) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S * half) return;
+  float c, s;
+  rope_sincos(freqs, i / half + freqs.position_offset, i % half, &c, &s);
+  table[i] = make_float2(c, s);
+}
+
 }  // namespace it

@@ -338,6 +338,15 @@ class raw:
         _lib.check(c.lib.it_linear_fwd(c.handle, c.stream(), n, in_dim, out_dim, x, w, y))
 
     @staticmethod
+    def qkv_rope_fwd(B, S, hidden, H, Hkv, D, base, position_offset, x, w_qkv, q, k, v, ctx=None):
+        c = ctx or context()
+        n = ctypes.c_size_t(0)
+        _lib.check(c.lib.it_qkv_rope_workspace_bytes(S, D, ctypes.byref(n)))
+        ws = _workspace(n.value)
+        _lib.check(c.lib.it_qkv_rope_fwd(c.handle, c.stream(), B, S, hidden, H, Hkv, D, float(base), int(position_offset), x,
+                                         w_qkv, q, k, v, ws.data_ptr(), ws.numel()))
+
+    @staticmethod
     def linear_bwd(n, in_dim, out_dim, dy, x, w, dx, dw, ctx=None):
         c = ctx or context()
         _lib.check(c.lib.it_linear_bwd(c.handle, c.stream(), n, in_dim, out_dim, dy, x, w, dx, dw))
@@ -549,6 +558,21 @@ def linear_forward(input, weight):
     y = Tensor.empty([n, out_dim], Precision.BF16)
     raw.linear_fwd(n, k, out_dim, input.data_ptr(), weight.data_ptr(), y.data_ptr())
     return y
+
+
+def qkv_rope_forward(x, w_qkv, heads, kv_heads, head_dim, rope_base=10000.0, position_offset=0):
+    """q_rope, k_rope, v from x [batch, seq, hidden] and the stacked weights [Wq; Wk; Wv] in one kernel: the three
+    projections of src/train/forward.rs:101-103 and the two rope() calls of :111-112, written directly in the
+    [batch, seq, heads, head_dim] layout attention_gqa reads.  rope_base None: no rotation."""
+    assert x.precision() is Precision.BF16 and w_qkv.precision() is Precision.BF16
+    B, S, hidden = x.shape()
+    assert w_qkv.shape() == [(heads + 2 * kv_heads) * head_dim, hidden], "w_qkv must be [Wq; Wk; Wv] stacked by rows"
+    q = Tensor.empty([B, S, heads, head_dim], Precision.BF16)
+    k = Tensor.empty([B, S, kv_heads, head_dim], Precision.BF16)
+    v = Tensor.empty([B, S, kv_heads, head_dim], Precision.BF16)
+    raw.qkv_rope_fwd(B, S, hidden, heads, kv_heads, head_dim, 0.0 if rope_base is None else rope_base, position_offset,
+                     x.data_ptr(), w_qkv.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr())
+    return q, k, v
 
 
 def linear_backward(grad_output, input, weight):

@@ -577,3 +577,28 @@ def test_projection_gemms_match_fp32_matmul(it_ctx, n, k, out):
         scale = np.abs(want).max() + 1e-30
         # bf16 results carry half an ulp (2^-9 relative) of storage rounding; the fp32 dW only accumulation error
         assert err <= (2e-5 if exact_store else 4.5e-3) * scale, f"{name} n={n} k={k} out={out}: {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("B,S,hidden,H,Hkv,D,base", [(2, 100, 256, 4, 2, 64, 10000.0), (1, 300, 512, 8, 8, 128, 10000.0),
+                                                      (3, 50, 64, 2, 1, 32, 500.0), (1, 130, 200, 3, 3, 96, None)])
+def test_fused_qkv_projection_with_rotary_epilogue(it_ctx, B, S, hidden, H, Hkv, D, base):
+    """qkv_rope_forward (one GEMM over [Wq; Wk; Wv] whose epilogue rotates Q and K and writes the attention layout)
+    against the reference's chain: three fp32 projections, then rope on Q and K (src/train/forward.rs:101-112)."""
+    from irontensor_b200 import Tensor, qkv_rope_forward
+    n, out = B * S, (H + 2 * Hkv) * D
+    x = synth.round_bf16(synth.normal(180, synth.TENSOR_Q, 0, n * hidden, 1.0)).reshape(B, S, hidden)
+    w = synth.round_bf16(synth.normal(180, synth.TENSOR_K, 0, out * hidden, 0.05)).reshape(out, hidden)
+    q, k, v = qkv_rope_forward(Tensor.from_f32_as_bf16(x.reshape(-1), [B, S, hidden]), Tensor.from_f32_as_bf16(w.reshape(-1), [out, hidden]),
+                               H, Hkv, D, base, 3)
+    assert it_ctx.poll_status() == 0
+    y = (x.reshape(n, hidden).astype(np.float64) @ w.astype(np.float64).T).astype(np.float32)
+    rq = y[:, :H * D].reshape(B, S, H, D)
+    rk = y[:, H * D:(H + Hkv) * D].reshape(B, S, Hkv, D)
+    rv = y[:, (H + Hkv) * D:].reshape(B, S, Hkv, D)
+    if base is not None:
+        rq, rk = ol.rope(rq, base, 3), ol.rope(rk, base, 3)
+    for got, want, name in ((q, rq, "q"), (k, rk, "k"), (v, rv, "v")):
+        g = got.to_f32_host()
+        assert g.shape == want.shape
+        err = np.abs(g - want).max()
+        assert err <= 4.5e-3 * np.abs(want).max(), f"{name}: {err}"
