@@ -169,9 +169,6 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 // Waits until all of this thread's bulk groups have completed, writes included.
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Barrier among `count` threads (a multiple of 32) that all name the same id (1..15).
-__device__ __forceinline__ void named_barrier_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
 
 // ---------------------------------------------------------------- tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
