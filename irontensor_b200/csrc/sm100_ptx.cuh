@@ -168,7 +168,6 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 }
 // Waits until all of this thread's bulk groups have completed, writes included.
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Barrier among `count` threads (a multiple of 32) that all name the same id (1..15).
 
 // ---------------------------------------------------------------- tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
