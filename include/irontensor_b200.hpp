@@ -381,4 +381,50 @@ inline Tensor attention_decode(const Tensor& q, const Tensor& k_cache, const Ten
   return out;
 }
 
+// output = input @ weight.T for BF16 tensors: input [n, in], weight [out, in] (src/train/helpers.rs:48-53).
+inline Tensor linear_forward(const Tensor& input, const Tensor& weight) {
+  require(input.precision() == Precision::BF16 && weight.precision() == Precision::BF16, "linear_forward takes BF16 tensors");
+  require(input.shape().size() == 2 && weight.shape().size() == 2 && input.shape()[1] == weight.shape()[1],
+          "inner dimensions must match");
+  Tensor y = Tensor::empty({input.shape()[0], weight.shape()[0]}, Precision::BF16);
+  check(it_linear_fwd(Context::global().raw(), Context::global().stream(), static_cast<int32_t>(input.shape()[0]),
+                      static_cast<int32_t>(input.shape()[1]), static_cast<int32_t>(weight.shape()[0]), input.ptr(), weight.ptr(),
+                      y.ptr()));
+  return y;
+}
+
+// (grad_input BF16 [n, in], grad_weight FP32 [out, in]) = (grad_output @ weight, grad_output.T @ input)
+// (src/train/helpers.rs:61-76; the reference returns FP32 gradients).
+inline std::pair<Tensor, Tensor> linear_backward(const Tensor& grad_output, const Tensor& input, const Tensor& weight) {
+  require(grad_output.shape().size() == 2 && input.shape().size() == 2 && weight.shape().size() == 2, "2D tensors expected");
+  const size_t n = grad_output.shape()[0], out = grad_output.shape()[1], in = input.shape()[1];
+  require(input.shape()[0] == n && weight.shape()[0] == out && weight.shape()[1] == in, "shape mismatch");
+  Tensor dx = Tensor::empty({n, in}, Precision::BF16), dw = Tensor::empty({out, in}, Precision::FP32);
+  check(it_linear_bwd(Context::global().raw(), Context::global().stream(), static_cast<int32_t>(n), static_cast<int32_t>(in),
+                      static_cast<int32_t>(out), grad_output.ptr(), input.ptr(), weight.ptr(), dx.ptr(),
+                      static_cast<float*>(dw.ptr())));
+  return {dx, dw};
+}
+
+// q_rope, k_rope, v from x [batch, seq, hidden] and the stacked weights [Wq; Wk; Wv] in one kernel
+// (src/train/forward.rs:101-103,111-112).  rope_base 0: no rotation.
+inline std::tuple<Tensor, Tensor, Tensor> qkv_rope_forward(const Tensor& x, const Tensor& w_qkv, size_t heads, size_t kv_heads,
+                                                           size_t head_dim, float rope_base = 10000.f, int position_offset = 0) {
+  require(x.shape().size() == 3 && w_qkv.shape().size() == 2, "x must be [batch, seq, hidden], w_qkv 2D");
+  const size_t B = x.shape()[0], S = x.shape()[1], hidden = x.shape()[2];
+  require(w_qkv.shape()[0] == (heads + 2 * kv_heads) * head_dim && w_qkv.shape()[1] == hidden,
+          "w_qkv must be [Wq; Wk; Wv] stacked by rows");
+  Tensor q = Tensor::empty({B, S, heads, head_dim}, Precision::BF16), k = Tensor::empty({B, S, kv_heads, head_dim}, Precision::BF16),
+         v = Tensor::empty({B, S, kv_heads, head_dim}, Precision::BF16);
+  size_t ws_bytes = 0;
+  check(it_qkv_rope_workspace_bytes(static_cast<int32_t>(S), static_cast<int32_t>(head_dim), &ws_bytes));
+  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  check(it_qkv_rope_fwd(Context::global().raw(), Context::global().stream(), static_cast<int32_t>(B), static_cast<int32_t>(S),
+                        static_cast<int32_t>(hidden), static_cast<int32_t>(heads), static_cast<int32_t>(kv_heads),
+                        static_cast<int32_t>(head_dim), rope_base, position_offset, x.ptr(), w_qkv.ptr(), q.ptr(), k.ptr(), v.ptr(),
+                        ws.ptr(), ws_bytes));
+  CommandBatch::sync();   // the table goes out of scope here
+  return {q, k, v};
+}
+
 }  // namespace it

@@ -233,6 +233,31 @@ int main() {
       std::vector<float> want(oh.begin() + (S - 1) * H * D, oh.begin() + S * H * D);
       EXPECT(max_abs_diff(dec.to_host_f32(), want) < 1e-5, "decode equals the last row");
     }
+    // --- projections: y = x W^T against a plain loop, and the fused Q/K/V front end against it
+    {
+      const size_t n = 96, in = 64, H = 2, Hkv = 1, D = 32, out = (H + 2 * Hkv) * D, B = 2, S = 48;
+      std::vector<float> x(n * in), w(out * in);
+      for (size_t i = 0; i < x.size(); ++i) x[i] = it::bf16_to_f32(it::f32_to_bf16(std::sin(0.13f * i)));
+      for (size_t i = 0; i < w.size(); ++i) w[i] = it::bf16_to_f32(it::f32_to_bf16(0.1f * std::cos(0.07f * i)));
+      std::vector<double> ref(n * out, 0.0);
+      for (size_t r = 0; r < n; ++r) for (size_t c = 0; c < out; ++c) for (size_t kk = 0; kk < in; ++kk)
+        ref[r * out + c] += static_cast<double>(x[r * in + kk]) * w[c * in + kk];
+      const Tensor tx = Tensor::from_f32_as_bf16(x, {n, in}), tw = Tensor::from_f32_as_bf16(w, {out, in});
+      const Tensor y = it::linear_forward(tx, tw);
+      EXPECT(max_abs_diff(y.to_host_f32(), ref) < 2e-2, "linear_forward");
+      auto [q, k, v] = it::qkv_rope_forward(tx.view({B, S, in}), tw, H, Hkv, D, 0.f);   // no rotation: pure layout
+      const std::vector<float> qh = q.to_host_f32(), vh = v.to_host_f32(), yh = y.to_host_f32();
+      double mq = 0, mv = 0;
+      for (size_t r = 0; r < n; ++r) {
+        for (size_t c = 0; c < H * D; ++c) mq = std::max(mq, std::fabs(static_cast<double>(qh[r * H * D + c]) - yh[r * out + c]));
+        for (size_t c = 0; c < Hkv * D; ++c)
+          mv = std::max(mv, std::fabs(static_cast<double>(vh[r * Hkv * D + c]) - yh[r * out + (H + Hkv) * D + c]));
+      }
+      EXPECT(mq == 0.0 && mv == 0.0, "fused projection without rotation equals the plain projection, column ranges split");
+      auto [dx, dw] = it::linear_backward(y, tx, tw);
+      EXPECT(dx.shape() == std::vector<size_t>({n, in}) && dw.shape() == std::vector<size_t>({out, in}) &&
+                 dw.precision() == Precision::FP32, "linear_backward shapes");
+    }
     // --- the reference's asserts
     {
       const Tensor a = Tensor::zeros({2, 4, 32, 16}), b = Tensor::zeros({2, 4, 33, 16});

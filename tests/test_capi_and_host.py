@@ -167,3 +167,20 @@ def test_head_parallel_projections_sum_to_the_full_layer_over_gloo(tmp_path):
                          capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "OK" in out.stdout
+
+
+def test_workspace_size_functions_of_the_widened_rows():
+    import ctypes
+    lib = _lib.load()
+    n = ctypes.c_size_t()
+    assert lib.it_attention_decode_workspace_bytes(32, 32, 128, ctypes.byref(n)) == _lib.IT_OK
+    assert n.value >= 32 * 32 * 64 * (128 + 2) * 4                    # 64 splits of (D + 2) floats per (batch, head)
+    assert lib.it_attention_decode_workspace_bytes(1, 1, 129, ctypes.byref(n)) == _lib.IT_ERR_UNSUPPORTED_SHAPE
+    assert lib.it_attention_decode_workspace_bytes(1, 1, 64, None) == _lib.IT_ERR_INVALID_ARG
+    assert lib.it_qkv_rope_workspace_bytes(8192, 128, ctypes.byref(n)) == _lib.IT_OK
+    assert n.value >= 8192 * 64 * 8                                   # one (cos, sin) pair per position and dimension pair
+    assert lib.it_qkv_rope_workspace_bytes(16, 63, ctypes.byref(n)) == _lib.IT_ERR_INVALID_ARG
+    # entry points that need a context refuse a null one before touching the GPU
+    assert lib.it_linear_fwd(None, None, 8, 8, 8, None, None, None) == _lib.IT_ERR_INVALID_ARG
+    assert lib.it_rope_qk(None, None, _lib.IT_F32, 1, 1, 1, 1, 8, 10000.0, 0, 0, None, None, None, None) == _lib.IT_ERR_INVALID_ARG
+    assert lib.it_attention_decode(None, None, _lib.IT_BF16, 1, 1, 1, 64, 1, 1, None, None, None, None, None, None, 0) == _lib.IT_ERR_INVALID_ARG

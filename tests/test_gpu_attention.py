@@ -514,7 +514,8 @@ def test_attention_backward_with_rope_folded_in(it_ctx, shape, bf16):
 @pytest.mark.parametrize("shape,bf16", [((2, 4, 4, 64, 100, 128), False), ((1, 8, 2, 128, 1000, 1024), False),
                                         ((3, 6, 2, 64, 777, 800), True), ((2, 32, 4, 128, 5000, 5000), True),
                                         ((1, 16, 1, 128, 4096, 4096), True), ((16, 4, 4, 64, 64, 256), True),
-                                        ((1, 2, 2, 40, 333, 400), False)])
+                                        ((1, 2, 2, 40, 333, 400), False), ((1, 128, 1, 64, 600, 640), True),
+                                        ((1, 160, 1, 64, 300, 300), True), ((2, 24, 2, 128, 257, 300), True)])
 def test_kv_cache_decode_equals_last_row_of_causal_attention(it_ctx, shape, bf16):
     """attention_decode (one new token against a K/V cache, grouped heads, keys split over CTAs) against the
     last row of the oracle's causal attention over the same kv_len tokens."""
