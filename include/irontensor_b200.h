@@ -199,12 +199,29 @@ it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_di
  * in the layout it_attention_gqa_* read.  The reference runs three linear_forward calls on the same input and
  * rope() twice (src/train/forward.rs:101-103,111-112).  rope_base 0 leaves Q and K un-rotated.  bf16; head_dim
  * 32, 64, 96 or 128; hidden a multiple of 8.  workspace (it_qkv_rope_workspace_bytes, 256-byte aligned; may be
- * null when rope_base is 0) holds the cosine/sine table of the call. */
+ * null when rope_base is 0) holds the cosine/sine table of the call.  With k_out and v_out both null, q_out is
+ * ONE packed buffer [batch, seq, (heads + 2*kv_heads)*head_dim] holding q_rope | k_rope | v per token: the layout
+ * it_attention_packed_* read, and whose gradient it_linear_bwd takes as a single dy. */
 it_status it_qkv_rope_workspace_bytes(int32_t seq, int32_t head_dim, size_t* out_bytes);
 it_status it_qkv_rope_fwd(it_ctx* ctx, it_stream* stream, int32_t batch, int32_t seq, int32_t hidden, int32_t heads,
                           int32_t kv_heads, int32_t head_dim, float rope_base, int32_t position_offset, const void* x,
                           const void* w_qkv, void* q_out, void* k_out, void* v_out, void* workspace,
                           size_t workspace_bytes);
+
+/* Attention on the packed projection output: qkv [batch, seq, (heads + 2*kv_heads)*head_dim] = q | k | v per token
+ * (what it_qkv_rope_fwd writes with k_out = v_out = null), o and d_o [batch, seq, heads, head_dim], dqkv in the
+ * layout of qkv.  Same kernels as it_attention_gqa_*: the column ranges are tensor-map strides.  With the
+ * projections on both sides this removes every layout step of the reference's layer (views, transposes, repeat_kv,
+ * the concatenation of the three gradients before the weight GEMMs): forward = it_qkv_rope_fwd, it_attention_packed_fwd,
+ * it_linear_fwd (Wo); backward = it_linear_bwd (Wo), it_attention_packed_bwd, it_linear_bwd (stacked [Wq; Wk; Wv]).
+ * rope_base as in it_attention_gqa_bwd_rope (0: none).  bf16, head_dim 64 or 128, seq >= 128. */
+it_status it_attention_packed_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq,
+                                  int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t causal, const void* qkv,
+                                  void* o, float* lse);
+it_status it_attention_packed_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq,
+                                  int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t causal, float rope_base,
+                                  int32_t position_offset, const void* qkv, const void* o, const void* d_o,
+                                  const float* lse, void* dqkv, void* workspace, size_t workspace_bytes);
 
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)

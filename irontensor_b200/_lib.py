@@ -49,6 +49,9 @@ SIGNATURES = {
     "it_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
     "it_attention_gqa_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "it_attention_gqa_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
+    "it_attention_packed_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+    "it_attention_packed_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _c.c_float, _i32, _vp, _vp, _vp, _vp, _vp,
+                                _vp, _c.c_size_t],
     "it_rope_qk": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _c.c_float, _i32, _i32, _vp, _vp, _vp, _vp],
     "it_attention_gqa_bwd_rope": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _c.c_float, _i32] + [_vp] * 9 +
                                  [_vp, _c.c_size_t],

@@ -47,6 +47,8 @@ struct GemmParams {
   // ranges are stored to q [M, heads, D], k and v [M, kv_heads, D].
   __nv_bfloat16 *q, *k, *v;
   int seq, heads, kv_heads, head_dim;
+  long long ld_q, ld_kv;      // elements between the rows (tokens) of q and of k / v: heads*D and kv_heads*D when the three are
+                              // separate tensors, (heads + 2 kv_heads)*D when they are column ranges of one packed buffer
   const float2* rope_table;   // [seq][head_dim / 2] (cos, sin), or null: no rotation
 };
 
@@ -214,15 +216,15 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             bool rotate = true;
             if (col < hd_total) {
               d0 = col % prm.head_dim;
-              dst = prm.q + (static_cast<long long>(row) * prm.heads + col / prm.head_dim) * prm.head_dim + d0;
+              dst = prm.q + static_cast<long long>(row) * prm.ld_q + col;
             } else if (col < hd_total + kv_total) {
               const int cc = col - hd_total;
               d0 = cc % prm.head_dim;
-              dst = prm.k + (static_cast<long long>(row) * prm.kv_heads + cc / prm.head_dim) * prm.head_dim + d0;
+              dst = prm.k + static_cast<long long>(row) * prm.ld_kv + cc;
             } else {
               const int cc = col - hd_total - kv_total;
               d0 = cc % prm.head_dim;
-              dst = prm.v + (static_cast<long long>(row) * prm.kv_heads + cc / prm.head_dim) * prm.head_dim + d0;
+              dst = prm.v + static_cast<long long>(row) * prm.ld_kv + cc;
               rotate = false;
             }
             if (rotate && prm.rope_table != nullptr) {

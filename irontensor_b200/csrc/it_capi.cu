@@ -191,14 +191,14 @@ void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
 template <int D, bool PP>
 it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, void* o, float* lse, const it::TensorStrides& stv,
-                           const it::TensorStrides& skv) {
+                           const it::TensorStrides& skv, const it::TensorStrides& sq) {
   const int BH = B * H;
   const int Hkv = H / skv.group;
   using T = std::conditional_t<PP, it::FwdPPTraits<D>, it::FwdTraits<D>>;
   auto kernel = PP ? it::fa_fwd_pp_sm100_kernel<D> : it::fa_fwd_sm100_kernel<D>;
   CUtensorMap mq, mk, mv;
   it_status st;
-  if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mq, q, B, H, S, D, sq, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mk, k, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mv, v, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   static bool attr_set[16] = {};
@@ -258,13 +258,13 @@ template <int D>
 it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk,
                            void* dv, uint8_t* ws, const BwdWorkspace& w, const it::TensorStrides& stv,
-                           const it::TensorStrides& skv, const it::RopeFreqs& rf) {
+                           const it::TensorStrides& skv, const it::RopeFreqs& rf, const it::TensorStrides& sq) {
   const int BH = B * H;
   const int Hkv = H / skv.group;
   using T = it::BwdTraits<D>;
   CUtensorMap mq, mk, mv, mdo;
   it_status st;
-  if ((st = make_tmap(ctx, &mq, q, B, H, S, D, stv, 128)) != IT_OK) return st;
+  if ((st = make_tmap(ctx, &mq, q, B, H, S, D, sq, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mk, k, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mv, v, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mdo, d_o, B, H, S, D, stv, 128)) != IT_OK) return st;
@@ -317,7 +317,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   }
   const size_t n4 = n_dq / 4;
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
-      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, stv, rf);
+      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, sq, rf);
   ctx->launches += 3;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -331,6 +331,7 @@ struct QkvEpilogue {
   void *q, *k, *v;
   int seq, heads, kv_heads, head_dim;
   const float2* rope_table;
+  long long ld_q, ld_kv;
 };
 
 template <int LAYOUT, bool QKV = false>
@@ -360,6 +361,7 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   p.status = ctx->d_status;
   p.q = p.k = p.v = nullptr;
   p.seq = p.heads = p.kv_heads = p.head_dim = 0;
+  p.ld_q = p.ld_kv = 0;
   p.rope_table = nullptr;
   if (epi != nullptr) {
     p.q = static_cast<__nv_bfloat16*>(epi->q);
@@ -370,6 +372,8 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
     p.kv_heads = epi->kv_heads;
     p.head_dim = epi->head_dim;
     p.rope_table = epi->rope_table;
+    p.ld_q = epi->ld_q;
+    p.ld_kv = epi->ld_kv;
   }
   const int n_tiles = ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
   const int grid = std::min(n_tiles, ctx->sm_count);
@@ -685,7 +689,7 @@ static it_status check_kv_heads(int32_t H, int32_t Hkv) {
 
 static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t Hkv,
                                     int32_t S, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
-                                    void* o, float* lse, bool bshd) {
+                                    void* o, float* lse, bool bshd, long long qkv_row = 0) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
   if (H > 0 && (st = check_kv_heads(H, Hkv)) != IT_OK) return st;
@@ -696,16 +700,23 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
     return fail(IT_ERR_ALIGNMENT, "q, k, v and o must be 16-byte aligned");
   IT_CUDA(cudaSetDevice(ctx->device));
   const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
-  const it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
+  it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
+  it::TensorStrides sq = sv;
+  if (qkv_row != 0) {   // q, k and v are column ranges of one [batch, seq, qkv_row] buffer
+    if (!use_sm100_path(dtype, S, D))
+      return fail(IT_ERR_UNSUPPORTED_SHAPE, "the packed layout needs bf16, head_dim 64 or 128 and seq >= 128");
+    sq.row = skv.row = qkv_row;
+    sq.batch = skv.batch = qkv_row * S;
+  }
   if (use_sm100_path(dtype, S, D)) {
     // Crossover measured on B200 (causal): equal at S = 4096, D = 128; the two-tile kernel wins below and
     // for D = 64 at every length.
     const bool pp = (D == 128) && (S >= 4096);
     if (D == 128)
-      return pp ? launch_fwd_sm100<128, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv)
-                : launch_fwd_sm100<128, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv);
-    return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv)
-              : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv);
+      return pp ? launch_fwd_sm100<128, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
+                : launch_fwd_sm100<128, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
+    return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
+              : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
   }
   if (dtype == IT_F32)
     launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
@@ -746,7 +757,7 @@ static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
                                     int32_t S, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
                                     const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
                                     void* workspace, size_t workspace_bytes, bool bshd,
-                                    const it::RopeFreqs& rf = make_rope_freqs(0, 1.f, 0, false)) {
+                                    const it::RopeFreqs& rf = make_rope_freqs(0, 1.f, 0, false), long long qkv_row = 0) {
   it_status st = check_common(ctx, stream, dtype, B, H, S, D);
   if (st != IT_OK) return st;
   if (H > 0 && (st = check_kv_heads(H, Hkv)) != IT_OK) return st;
@@ -766,11 +777,18 @@ static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
   IT_CUDA(cudaSetDevice(ctx->device));
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   const it::TensorStrides sv = bshd ? strides_bshd(H, S, D) : strides_bhsd(H, S, D);
-  const it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
+  it::TensorStrides skv = strides_kv(bshd, H, Hkv, S, D);
+  it::TensorStrides sq = sv;
+  if (qkv_row != 0) {   // q, k, v (and dq, dk, dv) are column ranges of one [batch, seq, qkv_row] buffer each
+    if (!use_sm100_path(dtype, S, D))
+      return fail(IT_ERR_UNSUPPORTED_SHAPE, "the packed layout needs bf16, head_dim 64 or 128 and seq >= 128");
+    sq.row = skv.row = qkv_row;
+    sq.batch = skv.batch = qkv_row * S;
+  }
   if (use_sm100_path(dtype, S, D)) {
     return D == 128
-               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf)
-               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf);
+               ? launch_bwd_sm100<128>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf, sq)
+               : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf, sq);
   }
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   if (dtype == IT_F32)
@@ -804,6 +822,16 @@ it_status it_attention_gqa_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, i
                             workspace_bytes, true);
 }
 
+it_status it_attention_packed_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H,
+                                  int32_t Hkv, int32_t D, int32_t causal, const void* qkv, void* o, float* lse) {
+  if (qkv == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (dtype != IT_BF16) return fail(IT_ERR_PRECISION, "the packed layout is bf16 only");
+  const long long row = (static_cast<long long>(H) + 2LL * Hkv) * D;
+  const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(qkv);
+  return attention_fwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, base, base + static_cast<long long>(H) * D,
+                            base + (static_cast<long long>(H) + Hkv) * D, o, lse, true, row);
+}
+
 static it_status check_rope(int32_t D, float base) {
   if (D < 2 || D > 128 || (D & 1)) return fail(IT_ERR_UNSUPPORTED_SHAPE, "rotary embedding needs an even head_dim in 2..128, got %d", D);
   if (!(base > 0.f)) return fail(IT_ERR_INVALID_ARG, "rotary base must be positive");
@@ -819,6 +847,23 @@ it_status it_attention_gqa_bwd_rope(it_ctx* ctx, it_stream* stream, it_dtype dty
   if (st != IT_OK) return st;
   return attention_bwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, workspace,
                             workspace_bytes, true, make_rope_freqs(D, rope_base, position_offset, true));
+}
+
+it_status it_attention_packed_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H,
+                                  int32_t Hkv, int32_t D, int32_t causal, float rope_base, int32_t position_offset,
+                                  const void* qkv, const void* o, const void* d_o, const float* lse, void* dqkv,
+                                  void* workspace, size_t workspace_bytes) {
+  if (qkv == nullptr || dqkv == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (dtype != IT_BF16) return fail(IT_ERR_PRECISION, "the packed layout is bf16 only");
+  it_status st;
+  if (rope_base != 0.f && (st = check_rope(D, rope_base)) != IT_OK) return st;
+  const long long row = (static_cast<long long>(H) + 2LL * Hkv) * D;
+  const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(qkv);
+  __nv_bfloat16* gbase = static_cast<__nv_bfloat16*>(dqkv);
+  const long long ko = static_cast<long long>(H) * D, vo = (static_cast<long long>(H) + Hkv) * D;
+  return attention_bwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, base, base + ko, base + vo, o, d_o, lse, gbase,
+                            gbase + ko, gbase + vo, workspace, workspace_bytes, true,
+                            make_rope_freqs(D, rope_base == 0.f ? 1.f : rope_base, position_offset, rope_base != 0.f), row);
 }
 
 it_status it_rope_qk(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t S, int32_t H, int32_t Hkv,
@@ -925,7 +970,8 @@ it_status it_qkv_rope_fwd(it_ctx* ctx, it_stream* stream, int32_t B, int32_t S, 
   const long long n = static_cast<long long>(B) * S;
   if (n == 0) return IT_OK;
   if (n > 0x7fffffffLL) return fail(IT_ERR_UNSUPPORTED_SHAPE, "too many tokens");
-  if (x == nullptr || w_qkv == nullptr || q_out == nullptr || k_out == nullptr || v_out == nullptr)
+  const bool packed = (k_out == nullptr && v_out == nullptr);   // q_out is then [batch, seq, (heads + 2 kv_heads) * head_dim]
+  if (x == nullptr || w_qkv == nullptr || q_out == nullptr || (!packed && (k_out == nullptr || v_out == nullptr)))
     return fail(IT_ERR_INVALID_ARG, "null tensor");
   if (!aligned16(x) || !aligned16(w_qkv) || !aligned16(q_out) || !aligned16(k_out) || !aligned16(v_out))
     return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
@@ -943,8 +989,14 @@ it_status it_qkv_rope_fwd(it_ctx* ctx, it_stream* stream, int32_t B, int32_t S, 
     ctx->launches += 1;
     table = static_cast<const float2*>(workspace);
   }
-  QkvEpilogue epi{q_out, k_out, v_out, S, H, Hkv, D, table};
   const int out_dim = (H + 2 * Hkv) * D;
+  QkvEpilogue epi{q_out, k_out, v_out, S, H, Hkv, D, table, static_cast<long long>(H) * D, static_cast<long long>(Hkv) * D};
+  if (packed) {
+    __nv_bfloat16* base = static_cast<__nv_bfloat16*>(q_out);
+    epi.k = base + static_cast<long long>(H) * D;
+    epi.v = base + (static_cast<long long>(H) + Hkv) * D;
+    epi.ld_q = epi.ld_kv = out_dim;
+  }
   return launch_gemm<0, true>(ctx, stream->s, static_cast<int>(n), out_dim, hidden, x, hidden, w_qkv, hidden, nullptr, 0,
                               false, &epi);
 }

@@ -347,6 +347,17 @@ class raw:
                                          w_qkv, q, k, v, ws.data_ptr(), ws.numel()))
 
     @staticmethod
+    def packed_fwd(B, S, H, Hkv, D, causal, qkv, o, lse, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_packed_fwd(c.handle, c.stream(), _lib.IT_BF16, B, S, H, Hkv, D, int(causal), qkv, o, lse))
+
+    @staticmethod
+    def packed_bwd(B, S, H, Hkv, D, causal, base, position_offset, qkv, o, d_o, lse, dqkv, ws, ws_bytes, ctx=None):
+        c = ctx or context()
+        _lib.check(c.lib.it_attention_packed_bwd(c.handle, c.stream(), _lib.IT_BF16, B, S, H, Hkv, D, int(causal), float(base),
+                                                 int(position_offset), qkv, o, d_o, lse, dqkv, ws, ws_bytes))
+
+    @staticmethod
     def linear_bwd(n, in_dim, out_dim, dy, x, w, dx, dw, ctx=None):
         c = ctx or context()
         _lib.check(c.lib.it_linear_bwd(c.handle, c.stream(), n, in_dim, out_dim, dy, x, w, dx, dw))
@@ -560,19 +571,50 @@ def linear_forward(input, weight):
     return y
 
 
-def qkv_rope_forward(x, w_qkv, heads, kv_heads, head_dim, rope_base=10000.0, position_offset=0):
+def qkv_rope_forward(x, w_qkv, heads, kv_heads, head_dim, rope_base=10000.0, position_offset=0, packed=False):
     """q_rope, k_rope, v from x [batch, seq, hidden] and the stacked weights [Wq; Wk; Wv] in one kernel: the three
     projections of src/train/forward.rs:101-103 and the two rope() calls of :111-112, written directly in the
-    [batch, seq, heads, head_dim] layout attention_gqa reads.  rope_base None: no rotation."""
+    [batch, seq, heads, head_dim] layout attention_gqa reads.  rope_base None: no rotation.  packed=True returns ONE
+    tensor [batch, seq, (heads + 2*kv_heads)*head_dim] (q_rope | k_rope | v per token) for attention_packed."""
     assert x.precision() is Precision.BF16 and w_qkv.precision() is Precision.BF16
     B, S, hidden = x.shape()
     assert w_qkv.shape() == [(heads + 2 * kv_heads) * head_dim, hidden], "w_qkv must be [Wq; Wk; Wv] stacked by rows"
+    if packed:
+        qkv = Tensor.empty([B, S, (heads + 2 * kv_heads) * head_dim], Precision.BF16)
+        raw.qkv_rope_fwd(B, S, hidden, heads, kv_heads, head_dim, 0.0 if rope_base is None else rope_base, position_offset,
+                         x.data_ptr(), w_qkv.data_ptr(), qkv.data_ptr(), None, None)
+        return qkv
     q = Tensor.empty([B, S, heads, head_dim], Precision.BF16)
     k = Tensor.empty([B, S, kv_heads, head_dim], Precision.BF16)
     v = Tensor.empty([B, S, kv_heads, head_dim], Precision.BF16)
     raw.qkv_rope_fwd(B, S, hidden, heads, kv_heads, head_dim, 0.0 if rope_base is None else rope_base, position_offset,
                      x.data_ptr(), w_qkv.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr())
     return q, k, v
+
+
+def attention_packed(qkv, heads, kv_heads, head_dim, causal=True):
+    """Grouped-query attention on the packed projection output [batch, seq, (heads + 2*kv_heads)*head_dim]
+    (qkv_rope_forward(..., packed=True)).  Returns O [batch, seq, heads, head_dim] with `.lse`."""
+    B, S, W = qkv.shape()
+    assert qkv.precision() is Precision.BF16 and W == (heads + 2 * kv_heads) * head_dim
+    out = Tensor.empty([B, S, heads, head_dim], Precision.BF16)
+    out.lse = Tensor.empty([B, heads, S], Precision.FP32)
+    raw.packed_fwd(B, S, heads, kv_heads, head_dim, causal, qkv.data_ptr(), out.data_ptr(), out.lse.data_ptr())
+    return out
+
+
+def attention_packed_backward(grad_output, qkv, o, heads, kv_heads, head_dim, causal=True, rope_base=None, position_offset=0):
+    """Gradient of attention_packed with respect to the packed tensor, in the same layout (dq | dk | dv per token, dk and dv
+    summed over each group, dq and dk rotated back when rope_base is given): ready to be the one `grad_output` of
+    linear_backward for the stacked weights [Wq; Wk; Wv]."""
+    B, S, W = qkv.shape()
+    assert grad_output.shape() == [B, S, heads, head_dim] and o.lse is not None
+    dqkv = Tensor.empty([B, S, W], Precision.BF16)
+    nbytes = raw.bwd_workspace_bytes(_lib.IT_BF16, B, heads, S, head_dim)
+    ws = _workspace(nbytes)
+    raw.packed_bwd(B, S, heads, kv_heads, head_dim, causal, 0.0 if rope_base is None else rope_base, position_offset,
+                   qkv.data_ptr(), o.data_ptr(), grad_output.data_ptr(), o.lse.data_ptr(), dqkv.data_ptr(), ws.data_ptr(), ws.numel())
+    return dqkv
 
 
 def linear_backward(grad_output, input, weight):

@@ -603,3 +603,42 @@ def test_fused_qkv_projection_with_rotary_epilogue(it_ctx, B, S, hidden, H, Hkv,
         assert g.shape == want.shape
         err = np.abs(g - want).max()
         assert err <= 4.5e-3 * np.abs(want).max(), f"{name}: {err}"
+
+
+@pytest.mark.parametrize("B,S,hidden,H,Hkv,D", [(2, 256, 128, 4, 2, 64), (1, 384, 256, 4, 4, 128), (1, 130, 64, 2, 1, 64)])
+def test_packed_layer_equals_the_separate_tensor_path(it_ctx, B, S, hidden, H, Hkv, D):
+    """The whole layer on ONE packed q|k|v buffer (fused projection -> attention -> attention backward with the rotary
+    backward folded in -> one linear_backward for the stacked weights) against the same ops on separate tensors with
+    the gradients concatenated by hand: identical forward, gradients within the dQ accumulation-order tolerance."""
+    from irontensor_b200 import (Tensor, attention_gqa, attention_gqa_backward, attention_packed, attention_packed_backward,
+                                 linear_backward, qkv_rope_forward)
+    n, W = B * S, (H + 2 * Hkv) * D
+    x = synth.round_bf16(synth.normal(190, synth.TENSOR_Q, 0, n * hidden, 1.0)).reshape(B, S, hidden)
+    w = synth.round_bf16(synth.normal(190, synth.TENSOR_K, 0, W * hidden, 0.08)).reshape(W, hidden)
+    d_o = synth.round_bf16(synth.normal(190, synth.TENSOR_DO, 0, n * H * D, 1.0)).reshape(B, S, H, D)
+    tx, tw = Tensor.from_f32_as_bf16(x.reshape(-1), [B, S, hidden]), Tensor.from_f32_as_bf16(w.reshape(-1), [W, hidden])
+    tdo = Tensor.from_f32_as_bf16(d_o.reshape(-1), [B, S, H, D])
+    base = 10000.0
+    # separate tensors
+    q, k, v = qkv_rope_forward(tx, tw, H, Hkv, D, base)
+    o = attention_gqa(q, k, v, True)
+    dq, dk, dv = attention_gqa_backward(tdo, q, k, v, o, True, rope_base=base)
+    cat = np.concatenate([dq.to_f32_host().reshape(n, H * D), dk.to_f32_host().reshape(n, Hkv * D),
+                          dv.to_f32_host().reshape(n, Hkv * D)], axis=1)
+    dx_ref, dw_ref = linear_backward(Tensor.from_f32_as_bf16(cat.reshape(-1), [n, W]), tx.view([n, hidden]), tw)
+    # packed
+    qkv = qkv_rope_forward(tx, tw, H, Hkv, D, base, packed=True)
+    o2 = attention_packed(qkv, H, Hkv, D, True)
+    dqkv = attention_packed_backward(tdo, qkv, o2, H, Hkv, D, True, rope_base=base)
+    dx, dw = linear_backward(dqkv.view([n, W]), tx.view([n, hidden]), tw)
+    assert it_ctx.poll_status() == 0
+    packed_host = qkv.to_f32_host().reshape(n, W)
+    assert np.array_equal(packed_host[:, :H * D], q.to_f32_host().reshape(n, H * D))
+    assert np.array_equal(packed_host[:, H * D:(H + Hkv) * D], k.to_f32_host().reshape(n, Hkv * D))
+    assert np.array_equal(packed_host[:, (H + Hkv) * D:], v.to_f32_host().reshape(n, Hkv * D))
+    assert np.array_equal(o2.to_f32_host(), o.to_f32_host()) and np.array_equal(o2.lse.to_f32_host(), o.lse.to_f32_host())
+    g = dqkv.to_f32_host().reshape(n, W)
+    assert np.array_equal(g[:, H * D:], cat[:, H * D:])                     # dk | dv: bit for bit
+    assert np.abs(g[:, :H * D] - cat[:, :H * D]).max() <= 2e-2              # dq: order of the fp32 reduce-adds
+    assert np.abs(dx.to_f32_host() - dx_ref.to_f32_host()).max() <= 4.5e-3 * np.abs(dx_ref.to_f32_host()).max() + 2e-2
+    assert np.abs(dw.to_f32_host() - dw_ref.to_f32_host()).max() <= 2e-2 * np.abs(dw_ref.to_f32_host()).max()
