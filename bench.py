@@ -428,6 +428,42 @@ def run_small(args):
                              "frac": flops / med / 1e6 / peaks["bf16"], "traffic": None}}
         print(json.dumps(line), flush=True)
         return
+    if args.workload == "layer":
+        # The whole attention layer of the C4 shape on the packed q|k|v layout: fused projection with rotary epilogue,
+        # attention, output projection; then the three backward steps.  No layout op anywhere.
+        from irontensor_b200 import Tensor, Precision, attention_packed, attention_packed_backward, linear_backward, linear_forward, \
+            qkv_rope_forward
+        B, S, hidden, H, Hkv, D = 4, 8192, 2048, 16, 16, 128
+        n, W = B * S, (H + 2 * Hkv) * D
+        mk = lambda shape, sc: Tensor((torch.randn(shape, generator=gen, device="cuda") * sc).to(torch.bfloat16).reshape(-1), list(shape),
+                                      Precision.BF16)
+        x, wqkv, wo, dout = mk((B, S, hidden), 1.0), mk((W, hidden), 0.02), mk((hidden, H * D), 0.02), mk((n, hidden), 1.0)
+
+        def f():
+            qkv = qkv_rope_forward(x, wqkv, H, Hkv, D, 10000.0, 0, packed=True)
+            attn = attention_packed(qkv, H, Hkv, D, True)
+            out = linear_forward(attn.view([n, H * D]), wo)
+            d_attn, d_wo = linear_backward(dout, attn.view([n, H * D]), wo)
+            d_qkv = attention_packed_backward(d_attn.view([B, S, H, D]), qkv, attn, H, Hkv, D, True, rope_base=10000.0)
+            d_x, d_wqkv = linear_backward(d_qkv.view([n, W]), x.view([n, hidden]), wqkv)
+            return out, d_wo, d_x, d_wqkv
+        for _ in range(max(args.warmup, 3)):
+            f()
+        l0 = ctx.launch_count()
+        med, mn = timed(f, args.steps, True)
+        launches = ctx.launch_count() - l0
+        gemm = 2.0 * n * hidden * (W + H * D)
+        flops = 3 * gemm + 7.0 * B * H * S * S * D
+        line = {"metric": "attention layer fwd+bwd TFLOP/s (projections + rotary + causal attention)", "unit": "TFLOP/s",
+                "value": flops / med / 1e6, "higher_is_better": True, "n_gpus": 1, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "dtype": "bf16", "data": "synthetic", "ms_per_step": med / 1e3,
+                "config": {"workload": "attention layer B4 S8192 hidden 2048, 16 heads of 128, packed q|k|v, bf16",
+                           "flops": {"projections": 3 * gemm, "attention": 7.0 * B * H * S * S * D}},
+                "gpu_launches": launches,
+                "roofline": {"bound": "tensor", "achieved": flops / med / 1e6, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                             "frac": flops / med / 1e6 / peaks["bf16"], "traffic": None}}
+        print(json.dumps(line), flush=True)
+        return
     # c5
     H, D = 4, 64
     lens = list(range(20, 120))
@@ -472,7 +508,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode", "linear"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode", "linear", "layer"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
     ap.add_argument("--slices", type=int, default=0,
@@ -489,7 +525,7 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", port, os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
-    if args.workload in ("c1", "c5", "decode", "linear"):
+    if args.workload in ("c1", "c5", "decode", "linear", "layer"):
         if rank == 0:
             run_small(args)
         return
