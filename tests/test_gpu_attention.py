@@ -642,3 +642,38 @@ def test_packed_layer_equals_the_separate_tensor_path(it_ctx, B, S, hidden, H, H
     assert np.abs(g[:, :H * D] - cat[:, :H * D]).max() <= 2e-2              # dq: order of the fp32 reduce-adds
     assert np.abs(dx.to_f32_host() - dx_ref.to_f32_host()).max() <= 4.5e-3 * np.abs(dx_ref.to_f32_host()).max() + 2e-2
     assert np.abs(dw.to_f32_host() - dw_ref.to_f32_host()).max() <= 2e-2 * np.abs(dw_ref.to_f32_host()).max()
+
+
+def test_randomised_shapes_against_the_oracle(it_ctx):
+    """Twenty seeded random shapes (ragged lengths around the 128-row tiles, odd batch and head counts, grouped heads,
+    both head dims of the tensor-core path and a few of the CUDA-core path, causal or not) through attention_gqa and
+    its backward, against the oracle composition.  Catches index arithmetic that the hand-picked shapes miss."""
+    from irontensor_b200 import Tensor, attention_gqa, attention_gqa_backward
+    rng = np.random.default_rng(20251)
+    for case in range(20):
+        D = int(rng.choice([64, 128, 128, 64, 32, 80]))
+        Hkv = int(rng.integers(1, 4))
+        G = int(rng.choice([1, 1, 2, 3, 4]))
+        H = Hkv * G
+        B = int(rng.integers(1, 3))
+        S = int(rng.choice([rng.integers(1, 130), rng.integers(128, 400), rng.integers(250, 700)]))
+        causal = bool(rng.integers(0, 2))
+        bf16 = True
+        q4, _, _, do4 = seeded(300 + case, B, H, S, D, bf16=bf16)
+        _, k4, v4, _ = seeded(400 + case, B, Hkv, S, D, bf16=bf16)
+        to_bshd = lambda a: np.ascontiguousarray(a.transpose(0, 2, 1, 3))
+        q, k, v, d_o = (to_bshd(a) for a in (q4, k4, v4, do4))
+        tq, tk, tv, tdo = (Tensor.from_f32_as_bf16(a.reshape(-1), list(a.shape)) for a in (q, k, v, d_o))
+        o = attention_gqa(tq, tk, tv, causal)
+        dq, dk, dv = attention_gqa_backward(tdo, tq, tk, tv, o, causal)
+        assert it_ctx.poll_status() == 0
+        ro, rlse = ol.gqa_fwd(q, k, v, causal)
+        rdq, rdk, rdv = ol.gqa_bwd(q, k, v, d_o, causal)
+        tag = f"case {case}: B{B} S{S} H{H} Hkv{Hkv} D{D} causal={causal}"
+        assert np.abs(o.lse.to_f32_host() - rlse).max() <= 1e-4, tag
+        for got, want, name in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+            # the 2e-2 bound on the absolute error is meant for values of order one: half a bf16 rounding step of an
+            # entry of magnitude 8 is already 3e-2 (short causal rows give such entries), so tensors whose largest entry exceeds 2 are
+            # brought to that range first; the relative L2 bounds are unaffected by the scaling
+            scale = max(1.0, float(np.abs(want).max()) / 2.0)
+            check_bf16(got.to_f32_host() / scale, want / scale, f"{tag} {name}")
