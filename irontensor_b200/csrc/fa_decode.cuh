@@ -115,15 +115,30 @@ fa_decode_split_kernel(const ST* __restrict__ q, const ST* __restrict__ k_cache,
   for (int k0 = k_begin; k0 < k_end; k0 += DEC_TK) {
     const int nk = min(DEC_TK, k_end - k0);
     __syncthreads();   // the previous tile's consumers are done (and s_q, s_m, s_l are set on the first pass)
-    for (int i = tid; i < DEC_TK * vec_per_row; i += DEC_THREADS) {
-      const int key = i / vec_per_row, c = i - key * vec_per_row;
-      uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;
-      if (key < nk) {
-        kk = *reinterpret_cast<const uint4*>(kb + static_cast<size_t>(k0 + key) * row_stride + c * VN);
-        vv = *reinterpret_cast<const uint4*>(vb + static_cast<size_t>(k0 + key) * row_stride + c * VN);
+    // eight 16-byte loads per thread are issued before the first is stored: the tile load is latency bound otherwise
+    constexpr int LB = 4;
+    for (int i0 = tid; i0 < DEC_TK * vec_per_row; i0 += DEC_THREADS * LB) {
+      uint4 kk[LB], vv[LB];
+#pragma unroll
+      for (int u = 0; u < LB; ++u) {
+        const int i = i0 + u * DEC_THREADS;
+        const int key = i / vec_per_row, c = i - key * vec_per_row;
+        kk[u] = make_uint4(0u, 0u, 0u, 0u);
+        vv[u] = kk[u];
+        if (i < DEC_TK * vec_per_row && key < nk) {
+          kk[u] = *reinterpret_cast<const uint4*>(kb + static_cast<size_t>(k0 + key) * row_stride + c * VN);
+          vv[u] = *reinterpret_cast<const uint4*>(vb + static_cast<size_t>(k0 + key) * row_stride + c * VN);
+        }
       }
-      *reinterpret_cast<uint4*>(s_k + key * RS + c * VN) = kk;
-      *reinterpret_cast<uint4*>(s_v + key * RS + c * VN) = vv;
+#pragma unroll
+      for (int u = 0; u < LB; ++u) {
+        const int i = i0 + u * DEC_THREADS;
+        if (i < DEC_TK * vec_per_row) {
+          const int key = i / vec_per_row, c = i - key * vec_per_row;
+          *reinterpret_cast<uint4*>(s_k + key * RS + c * VN) = kk[u];
+          *reinterpret_cast<uint4*>(s_v + key * RS + c * VN) = vv[u];
+        }
+      }
     }
     __syncthreads();
     // scores: thread = (key, every other head)
