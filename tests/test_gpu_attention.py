@@ -253,6 +253,42 @@ def test_config4_long_context_bf16(it_ctx):
     assert ((lhs - rhs).abs().max() / rhs.abs().max()).item() < 2e-2
 
 
+@pytest.mark.parametrize("shape", [(1, 2, 32768, 128), (1, 1, 65536, 128), (1, 2, 40000, 64)])
+def test_sequences_beyond_the_bench_size(it_ctx, shape):
+    """Sequences of 32K-64K keys (hundreds of key tiles per query tile): checked through properties that
+    need no O(S^2) oracle run, plus the first rows against an fp32 softmax (causal rows see only their prefix)."""
+    import torch
+    B, H, S, D = shape
+    gen = torch.Generator(device="cuda").manual_seed(synth.BASE_SEED + S)
+    q, k, v, d_o = [torch.randn(B, H, S, D, device="cuda", generator=gen).mul_(0.5 if i < 2 else 1.0).to(torch.bfloat16)
+                    for i in range(4)]
+    o = torch.full_like(q, float("nan"))
+    lse = torch.full((B, H, S), float("nan"), device="cuda")
+    ones = torch.ones_like(v)
+    raw.fwd(_lib.IT_BF16, B, H, S, D, True, q.data_ptr(), k.data_ptr(), ones.data_ptr(), o.data_ptr(), lse.data_ptr(),
+            ctx=it_ctx)
+    assert it_ctx.poll_status() == 0
+    assert (o.float() - 1).abs().max().item() <= 2 ** -7
+    raw.fwd(_lib.IT_BF16, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+            ctx=it_ctx)
+    g = [torch.full_like(q, float("nan")) for _ in range(3)]
+    n = raw.bwd_workspace_bytes(_lib.IT_BF16, B, H, S, D)
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    raw.bwd(_lib.IT_BF16, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+            lse.data_ptr(), g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), ws.data_ptr(), n, ctx=it_ctx)
+    assert it_ctx.poll_status() == 0
+    for t in (o, lse, *g):
+        assert not torch.isnan(t).any().item()
+    lhs, rhs = g[2].float().sum(2), d_o.float().sum(2)
+    assert ((lhs - rhs).abs().max() / rhs.abs().max()).item() < 1e-3
+    R = 256
+    s = torch.einsum("bhqd,bhkd->bhqk", q[:, :, :R].float(), k[:, :, :R].float()) / D ** 0.5
+    s = s.masked_fill(torch.ones(R, R, device="cuda").triu(1).bool(), float("-inf"))
+    want = torch.softmax(s, -1) @ v[:, :, :R].float()
+    assert (o[:, :, :R].float() - want).abs().max().item() <= 2e-2
+    assert (lse[:, :, :R] - torch.logsumexp(s, -1)).abs().max().item() <= 1e-3
+
+
 def test_causality_and_determinism(it_ctx):
     q, k, v, d_o = seeded(55, 1, 2, 512, 128, bf16=True)
     o1, l1 = gu.run_fwd(it_ctx, q, k, v, True, True)
