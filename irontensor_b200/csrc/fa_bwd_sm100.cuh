@@ -210,17 +210,17 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int lane = threadIdx.x & 31;
   const int S = prm.S;
   const int n_q_tiles = (S + T::BN - 1) / T::BN;
-  // Head-major order: the CTAs resident at one time belong to two or three (batch, head) slices, so
-  // their Q/dO streams and the fp32 dQ accumulator they add into stay in L2.  Within a slice key
-  // tile 0 comes first: under the causal mask it sees every query tile and has the most work.
+  // Head-major order in groups of four slices (grouped_tile_order): the CTAs resident at one time belong
+  // to four (batch, head) slices, so their Q/dO streams and the fp32 dQ accumulator they add into stay in
+  // L2.  Key tile 0 comes first: under the causal mask it sees every query tile and has the most work.
   const int n_k_tiles = (S + T::BM - 1) / T::BM;
   // A CTA owns one key tile of one K/V head and loops over the query heads of that head's group
   // (grouped-query attention: dK and dV are the sums over the group, accumulated in TMEM, so the
   // reference's repeat_kv_backward pass, src/shaders/repeat_kv.metal:49-88, does not exist here).
   const int G = prm.st_kv.group;
   const int kv_heads = prm.st.heads / G;
-  const int bhk = static_cast<int>(blockIdx.x) / n_k_tiles;   // batch * kv_heads + kv_head
-  const int kt = static_cast<int>(blockIdx.x) % n_k_tiles;
+  int bhk, kt;   // batch * kv_heads + kv_head, key tile
+  grouped_tile_order(static_cast<int>(blockIdx.x), n_k_tiles, static_cast<int>(gridDim.x) / n_k_tiles, &bhk, &kt);
   const int hkv = bhk % kv_heads, bt = bhk / kv_heads;        // TMA coordinates of the K/V slice
   const int bh0 = bt * prm.st.heads + hkv * G;                // first query slice of the group
   const int i0 = prm.causal ? kt : 0;

@@ -20,4 +20,20 @@ struct TensorStrides {
   __host__ __device__ long long slice(int bh) const { return (bh / heads) * batch + ((bh % heads) / group) * head; }
 };
 
+// Order in which the CTAs of a causal launch are handed out.  A CTA's work grows with its tile index
+// rank (0 = most work).  Slice after slice, heaviest tile first, keeps the resident CTAs on two or three
+// slices (good for L2) but ends badly: the last slice's heaviest CTA starts when little other work is
+// left and the other SMs idle while it runs (3.3 % of the launch at 64 slices x 64 tiles on 148 SMs).
+// Taking the slices four at a time and, inside such a group, all rank-0 tiles first, then all rank-1
+// tiles, ... brings that tail to 0.4 % and keeps the resident set at four slices.
+__device__ inline void grouped_tile_order(int block, int n_tiles, int n_slices, int* slice, int* rank) {
+  constexpr int GROUP = 4;
+  const int per_group = GROUP * n_tiles;
+  const int s0 = (block / per_group) * GROUP;
+  const int rem = block % per_group;
+  const int gsize = min(GROUP, n_slices - s0);
+  *rank = rem / gsize;
+  *slice = s0 + rem % gsize;
+}
+
 }  // namespace it
