@@ -15,7 +15,7 @@ Prints ONE JSON line:
                the causal-halved FlashAttention convention), device time from CUDA events, max over ranks
   e2e          the same metric through the package's public ops with HOST tensors (HostAttentionStep):
                every step uploads Q,K,V,dO from pinned memory and downloads O,dQ,dK,dV inside the timed
-               region, slices in 8 groups on rotating streams so copies and kernels overlap
+               region, slices in 16 groups on rotating streams so copies and kernels overlap
   roofline     the backward main kernel (dominant) against the measured dense-bf16 peak
   cpu_baseline the CPU oracle timed on this box's host cores on a bounded sample (rank 0, N=1 only)
 --impl reference times the reference's algorithm on the host cores instead (the CPU oracle: the
@@ -257,7 +257,7 @@ def run_ours(args, rank, world, local_rank):
     hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, d_o))
     ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
     from irontensor_b200 import HostAttentionStep
-    pipe = HostAttentionStep(n, S, D, Precision.BF16, causal=True, chunks=8)
+    pipe = HostAttentionStep(n, S, D, Precision.BF16, causal=True, chunks=args.e2e_chunks)
 
     def step_e2e():
         pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv)
@@ -533,6 +533,9 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode", "linear", "layer"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
+    ap.add_argument("--e2e-chunks", type=int, default=16,
+                    help="groups the end-to-end leg cuts a rank's slices into (upload, kernels and download of "
+                         "different groups overlap)")
     ap.add_argument("--slices", type=int, default=0,
                     help="use only this many (batch x head) slices of the workload (small profiling cases)")
     args = ap.parse_args()

@@ -75,54 +75,64 @@ struct BwdParams {
 };
 
 // ------------------------------------------------------------------ (1) prepare
-// One warp per four consecutive rows of one (batch, head): delta and LSE*log2e into the padded arrays, and
+// One warp per eight consecutive rows of one (batch, head): delta and LSE*log2e into the padded arrays, and
 // the rows' slices of the fp32 dQ accumulator cleared (saves a separate pass over those 4*D bytes per
-// row).  All eight loads of a lane are issued before the first is used: with one row per warp the
-// kernel ran at 70 % of the HBM rate for want of bytes in flight.
+// row).  A row is read by 16 lanes (16 bytes per lane at head_dim 128, 8 at 64), so a warp covers two
+// rows per load; all eight loads of a lane are issued before the first is used (with one row per warp
+// the kernel ran at 70 % of the HBM rate for want of bytes in flight, and 4-byte loads at head_dim 64
+// kept half as many bytes in flight as at 128).
 template <int D>
 __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       const float* __restrict__ lse, float* __restrict__ lse2_pad,
                                       float* __restrict__ delta_pad, float* __restrict__ dq_accum, int S, int S_pad,
                                       int BH, ptx::TensorStrides st) {
-  constexpr int RW = 4;            // rows per warp; S_pad is a multiple of 128, so the four rows share a head
-  constexpr int EL = D / 32;       // elements per lane and row: 4 (D = 128) or 2 (D = 64)
+  constexpr int NP = 4;            // passes; a pass covers two rows, one per half-warp
+  constexpr int RW = 2 * NP;       // rows per warp; S_pad is a multiple of 128, so they share a head
+  constexpr int EL = D / 16;       // elements per lane and row: 8 (D = 128) or 4 (D = 64)
   const int lane = threadIdx.x & 31;
+  const int sub = lane & 15, half = lane >> 4;
   const long long row0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * RW;
   if (row0 >= static_cast<long long>(BH) * S_pad) return;
   const int bh = static_cast<int>(row0 / S_pad);
   const int s0 = static_cast<int>(row0 % S_pad);
-  uint2 a[RW], b[RW];
+  uint4 a[NP], b[NP];
 #pragma unroll
-  for (int r = 0; r < RW; ++r) {
-    a[r] = make_uint2(0u, 0u);
-    b[r] = make_uint2(0u, 0u);
-    if (s0 + r < S) {
-      const size_t base = static_cast<size_t>(st.slice(bh) + static_cast<long long>(s0 + r) * st.row);
-      if (EL == 4) {
-        a[r] = reinterpret_cast<const uint2*>(o + base)[lane];
-        b[r] = reinterpret_cast<const uint2*>(d_o + base)[lane];
+  for (int r = 0; r < NP; ++r) {
+    a[r] = make_uint4(0u, 0u, 0u, 0u);
+    b[r] = make_uint4(0u, 0u, 0u, 0u);
+    const int s_ = s0 + 2 * r + half;
+    if (s_ < S) {
+      const size_t base = static_cast<size_t>(st.slice(bh) + static_cast<long long>(s_) * st.row);
+      if (EL == 8) {
+        a[r] = reinterpret_cast<const uint4*>(o + base)[sub];
+        b[r] = reinterpret_cast<const uint4*>(d_o + base)[sub];
       } else {
-        a[r].x = reinterpret_cast<const uint32_t*>(o + base)[lane];
-        b[r].x = reinterpret_cast<const uint32_t*>(d_o + base)[lane];
+        const uint2 ta = reinterpret_cast<const uint2*>(o + base)[sub];
+        const uint2 tb = reinterpret_cast<const uint2*>(d_o + base)[sub];
+        a[r].x = ta.x, a[r].y = ta.y;
+        b[r].x = tb.x, b[r].y = tb.y;
       }
     }
   }
   float lse_r = 0.f;
   if (lane < RW && s0 + lane < S) lse_r = lse[static_cast<size_t>(bh) * S + s0 + lane];
 #pragma unroll
-  for (int r = 0; r < RW; ++r) {
-    if (s0 + r < S) {
-      float* acc_row = dq_accum + (static_cast<size_t>(bh) * S + s0 + r) * D;   // the accumulator is always [BH, S, D]
-      if (EL == 4) {
-        reinterpret_cast<float4*>(acc_row)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < NP; ++r) {
+    const int s_ = s0 + 2 * r + half;
+    if (s_ < S) {
+      float* acc_row = dq_accum + (static_cast<size_t>(bh) * S + s_) * D;   // the accumulator is always [BH, S, D]
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (EL == 8) {   // 512 bytes per row: two 256-byte halves, each written by the 16 lanes at once
+        reinterpret_cast<float4*>(acc_row)[sub] = z;
+        reinterpret_cast<float4*>(acc_row)[16 + sub] = z;
       } else {
-        reinterpret_cast<float2*>(acc_row)[lane] = make_float2(0.f, 0.f);
+        reinterpret_cast<float4*>(acc_row)[sub] = z;
       }
     }
   }
-  float acc[RW];
+  float acc[NP];
 #pragma unroll
-  for (int r = 0; r < RW; ++r) {
+  for (int r = 0; r < NP; ++r) {
     const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a[r]);
     const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b[r]);
     acc[r] = 0.f;
@@ -134,15 +144,18 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
     }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
+  for (int off = 8; off > 0; off >>= 1) {
 #pragma unroll
-    for (int r = 0; r < RW; ++r) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+    for (int r = 0; r < NP; ++r) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+  }
+  // row s0 + j (j < 8) was summed in pass j / 2 by half-warp j & 1: bring it to lane j
+  float d = 0.f;
+#pragma unroll
+  for (int r = 0; r < NP; ++r) {
+    const float t = __shfl_sync(0xffffffffu, acc[r], (lane & 1) * 16);
+    if ((lane >> 1) == r) d = t;
   }
   if (lane < RW) {
-    float d = acc[0];
-#pragma unroll
-    for (int r = 1; r < RW; ++r)
-      if (lane == r) d = acc[r];
     const bool valid = s0 + lane < S;
     delta_pad[row0 + lane] = valid ? d : 0.f;
     lse2_pad[row0 + lane] = valid ? lse_r * 1.4426950408889634f : INFINITY;

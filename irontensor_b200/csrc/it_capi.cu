@@ -290,7 +290,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   const size_t n_dq = static_cast<size_t>(BH) * S * D;
   const long long rows_pad = static_cast<long long>(BH) * w.S_pad;
-  it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad / 4 + 7) / 8), 256, 0, s>>>(
+  it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad / 8 + 7) / 8), 256, 0, s>>>(   // 8 rows per warp, 8 warps
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, dq_accum, S,
       w.S_pad, BH, stv);
   it::BwdParams p;
