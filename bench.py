@@ -300,7 +300,9 @@ def run_ours(args, rank, world, local_rank):
     }
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms),
+                                                "first": step_ms[0], "last": step_ms[-1], "note": "rank 0's timed steps"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": desc, "sharding": f"{BH} (batch x head) slices split contiguously over {world} GPU(s), no collective",
                    "l2": "256 MB buffer written between timed steps; per-GPU tensors exceed L2 at N=1",
