@@ -64,6 +64,29 @@ def measured_peaks():
     return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
 
 
+def bind_host_to_gpu(gpu_index):
+    """Runs this process on the CPU cores next to the GPU (NVML's affinity mask for it), so that the
+    page-locked host tensors of the end-to-end leg are allocated in that socket's memory and the
+    copies do not cross the inter-socket link.  Changes only this process's own affinity; returns a
+    description for the JSON line, or why nothing was changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(int(gpu_index))
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (max(allowed) // 64) + 1)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        use = allowed & near
+        if not use:
+            return "no allowed core next to the GPU: affinity unchanged"
+        if use == allowed:
+            return f"all {len(allowed)} allowed cores are next to the GPU"
+        os.sched_setaffinity(0, use)
+        return f"{len(use)} of {len(allowed)} allowed cores (those next to the GPU)"
+    except Exception as e:   # NVML missing or refusing: measure with the default placement
+        return f"affinity unchanged ({type(e).__name__})"
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
 
@@ -166,6 +189,9 @@ def run_ours(args, rank, world, local_rank):
     from irontensor_b200 import _lib
     from irontensor_b200.sharding import shard_range
 
+    all_cores = os.sched_getaffinity(0)
+    host_binding = "off" if args.no_bind else bind_host_to_gpu(
+        local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
     torch.cuda.set_device(local_rank)
     ctx = context(local_rank)
     B, H, S, D, qs, desc = WORKLOADS[args.workload]
@@ -308,12 +334,14 @@ def run_ours(args, rank, world, local_rank):
                    "l2": "256 MB buffer written between timed steps; per-GPU tensors exceed L2 at N=1",
                    "tflops_per_gpu": value / world, "frac_of_bf16_peak_per_gpu": value / world / peaks["bf16"]},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * nbytes,
-                "d2h_bytes_per_step": 4 * nbytes, "note": "bytes are rank 0's"},
+                "d2h_bytes_per_step": 4 * nbytes, "note": "bytes are rank 0's", "groups": args.e2e_chunks,
+                "host_cores": host_binding},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roofline,
     }
     if world == 1 and not args.no_cpu:
+        os.sched_setaffinity(0, all_cores)   # the CPU baseline uses every core the process was given
         n_slices = 4 if S >= 4096 else min(BH, 32)
         r, dt, cores = cpu_oracle_rate(S, D, qs, n_slices, 0x1A7E5EED + 4)
         line["cpu_baseline"] = {"value": r, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -535,6 +563,7 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c1", "c5", "decode", "linear", "layer"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
+    ap.add_argument("--no-bind", action="store_true", help="leave the process's CPU affinity alone")
     ap.add_argument("--e2e-chunks", type=int, default=16,
                     help="groups the end-to-end leg cuts a rank's slices into (upload, kernels and download of "
                          "different groups overlap)")
