@@ -159,25 +159,25 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
 
 // fp32 tensors with D a multiple of 4 and short to medium sequences: the latency path (the greedy
 // no-KV-cache inference pattern re-runs it once per generated token, and the reference's TINY model
-// sits at S = 256).  A CTA owns 16 consecutive query rows of one head, four per warp.  Keys and
+// sits at S = 256).  A CTA owns 16 consecutive query rows of one head, RW (four or two) per warp.  Keys and
 // values stream through shared memory 32 at a time (cp.async, double buffered, rows padded by four
 // floats so that lane-per-key float4 reads are conflict free).  Scores: one key per lane, each K
-// chunk read once and used for the warp's four rows; softmax: online, warp-reduced per tile (the
+// chunk read once and used for all of the warp's rows; softmax: online, warp-reduced per tile (the
 // recurrence of src/shaders/flash_attention.metal:27-41); output: lanes over the head dimension,
 // the tile's probabilities parked in shared memory and read back four keys at a time, V read from
 // shared memory.  NJ = ceil(D / 32) output elements per lane.
-template <int NJ>
-__global__ void __launch_bounds__(128)
+template <int NJ, int RW>
+__global__ void __launch_bounds__(32 * (16 / RW))
 fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                        float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
                        TensorStrides st, TensorStrides skv) {
-  constexpr int RB = 16, RW = 4, TK = 32;
+  constexpr int RB = 16, TK = 32, NT = 32 * (RB / RW);   // RB / RW warps, RW rows each
   extern __shared__ __align__(16) float sm[];
   const int DS = D + 4;                       // padded row stride (floats)
   float* sQ = sm;                             // [RB][D]
   float* sK = sQ + RB * D;                    // [2][TK][DS]
   float* sV = sK + 2 * TK * DS;               // [2][TK][DS]
-  float* sP = sV + 2 * TK * DS;               // [4 warps][RW][TK] probabilities of the current tile
+  float* sP = sV + 2 * TK * DS;               // [warps][RW][TK] probabilities of the current tile
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nd4 = D >> 2;
   const int n_rb = (S + RB - 1) / RB;
@@ -195,7 +195,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
     const int k0 = tile * TK;
     float* dk = sK + buf * TK * DS;
     float* dv = sV + buf * TK * DS;
-    for (int idx = tid; idx < TK * nd4; idx += 128) {
+    for (int idx = tid; idx < TK * nd4; idx += NT) {
       const int key = idx / nd4, c = idx - key * nd4;
       float* pk = dk + key * DS + 4 * c;
       float* pv = dv + key * DS + 4 * c;
@@ -212,7 +212,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
   };
 
   load_tile(0, 0);
-  for (int idx = tid; idx < RB * nd4; idx += 128) {
+  for (int idx = tid; idx < RB * nd4; idx += NT) {
     const int rr = idx / nd4, c = idx - rr * nd4;
     float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r0 + rr < S) val = reinterpret_cast<const float4*>(q + base + static_cast<size_t>(r0 + rr) * RS)[c];
@@ -221,12 +221,14 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
 
   float m_run[RW], l_run[RW], acc[RW][NJ];
   int lim[RW];                                  // last visible key of each of this warp's rows
+  int lim_max = -1;
 #pragma unroll
   for (int w = 0; w < RW; ++w) {
     const int row = r0 + warp * RW + w;
     m_run[w] = -INFINITY;
     l_run[w] = 0.f;
     lim[w] = (row < S) ? (causal ? row : S - 1) : -1;
+    lim_max = max(lim_max, lim[w]);
 #pragma unroll
     for (int jj = 0; jj < NJ; ++jj) acc[w][jj] = 0.f;
   }
@@ -241,10 +243,12 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
     }
     __syncthreads();
     const int k0 = tile * TK;
-    if (k0 <= max(max(lim[0], lim[1]), max(lim[2], lim[3]))) {   // some row of this warp sees a key of the tile
+    if (k0 <= lim_max) {   // some row of this warp sees a key of the tile
       const float4* kp = reinterpret_cast<const float4*>(sK + buf * TK * DS + lane * DS);
       const float4* qp = reinterpret_cast<const float4*>(sQ + warp * RW * D);
-      float dot[RW] = {0.f, 0.f, 0.f, 0.f}, dot2[RW] = {0.f, 0.f, 0.f, 0.f};
+      float dot[RW], dot2[RW];
+#pragma unroll
+      for (int w = 0; w < RW; ++w) dot[w] = dot2[w] = 0.f;
 #pragma unroll 4
       for (int c = 0; c < nd4; ++c) {
         const float4 kv = kp[c];
