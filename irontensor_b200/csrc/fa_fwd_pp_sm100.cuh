@@ -115,18 +115,12 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     j0 = sp * prm.dec_tiles_per_split;
     nkv = max(0, min(prm.dec_tiles_per_split, n_kv_total - j0));
   } else {
-    // Launches of fewer than 4096 CTAs (a shard of the slices on one of several GPUs) take the slices
-    // four at a time, heaviest query tiles of all four first: slice after slice, the last slice's
-    // 64-tile CTA would run almost alone (28 % of the launch at 8 slices of 64 tiles on 148 SMs, 5 % in
-    // groups).  From 4096 CTAs on the two orders measured the same and the plain one is kept.
-    if (gridDim.x < 4096u) {
-      int rank;
-      grouped_tile_order(static_cast<int>(blockIdx.x), n_qt, static_cast<int>(gridDim.x) / n_qt, &bh, &rank);
-      qt = n_qt - 1 - rank;
-    } else {
-      bh = static_cast<int>(blockIdx.x) / n_qt;
-      qt = n_qt - 1 - static_cast<int>(blockIdx.x) % n_qt;
-    }
+    // Slice after slice, except that the last eight slices are taken together, heaviest query tiles of
+    // all eight first (tail_grouped_order): otherwise the last slice's 64-tile CTA runs almost alone
+    // (3 % of a 64-slice launch, 28 % of the 8-slice launch one of eight GPUs gets).
+    int rank;
+    tail_grouped_order(static_cast<int>(blockIdx.x), n_qt, static_cast<int>(gridDim.x) / n_qt, &bh, &rank);
+    qt = n_qt - 1 - rank;
     hd = bh % prm.st.heads;   // TMA coordinates of the slice
     bt = bh / prm.st.heads;
     hkv = hd / prm.kv_group;  // the K/V head this query head reads

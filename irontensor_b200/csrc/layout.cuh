@@ -36,4 +36,22 @@ __device__ inline void grouped_tile_order(int block, int n_tiles, int n_slices, 
   *slice = s0 + rem % gsize;
 }
 
+// The same idea for a kernel that is sensitive to how many slices are resident at once (the forward
+// streams K/V tiles from L2, and CTAs of one slice share them): slice after slice as long as enough
+// slices follow to fill the tail, and only the last eight slices taken together, heaviest tiles first.
+// The model gives the same tails as groups of four everywhere (0.4 % at 64 slices, 5 % at 8).
+__device__ inline void tail_grouped_order(int block, int n_tiles, int n_slices, int* slice, int* rank) {
+  constexpr int TAIL = 8;
+  const int head = max(n_slices - TAIL, 0);
+  if (block < head * n_tiles) {
+    *slice = block / n_tiles;
+    *rank = block % n_tiles;
+  } else {
+    const int rem = block - head * n_tiles;
+    const int t = n_slices - head;
+    *rank = rem / t;
+    *slice = head + rem % t;
+  }
+}
+
 }  // namespace it
