@@ -91,10 +91,11 @@ class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
 
     def __init__(self, gpu_index):
         self.lines = []
+        self.t0 = 0.0
         self.proc = None
         self.gpu_index = gpu_index
 
@@ -102,40 +103,62 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark(self):
+        """Samples that arrived before this call are left out (nvidia-smi needs ~0.1 s to start)."""
+        self.t0 = time.time()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        t1 = time.time()     # samples that arrive later belong to the idle time after the region
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], None, set()
+        sm, watts, mx, reasons = [], [], None, set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        for t, ln in self.lines:
+            if t < self.t0 or t > t1 + 0.005:
+                continue
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 6:
                 continue
             try:
-                sm.append(float(parts[0]))
+                clk = float(parts[0])
                 mx = float(parts[1])
             except ValueError:
                 continue
+            try:
+                w = float(parts[6])
+            except (IndexError, ValueError):
+                w = None
+            sm.append(clk)
+            watts.append(w)
             for name, val in zip(names, parts[2:6]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+               "samples": len(sm)}
+        known = [w for w in watts if w is not None]
+        if known:
+            # nvidia-smi's power figure is averaged over about a second, so it lags a timed region of
+            # ~0.1 s; "under load" = samples drawing at least 70 % of the highest power seen
+            top = max(known)
+            loaded = [c for c, w in zip(sm, watts) if w is not None and w >= 0.7 * top]
+            out.update({"power_w_max": top, "sm_mhz_under_load": statistics.median(loaded) if loaded else None,
+                        "sm_mhz_min": min(sm), "samples_under_load": len(loaded)})
+        return out
 
 
 def cpu_oracle_rate(S, D, qk_scale, n_slices, seed):
@@ -250,7 +273,8 @@ def run_ours(args, rank, world, local_rank):
     launches0 = ctx.launch_count()
     barrier()
     sampler.start()
-    time.sleep(0.1)
+    time.sleep(0.15)
+    sampler.mark()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     fwd_ms, bwd_ms = [], []
     for i in range(steps):
@@ -271,8 +295,8 @@ def run_ours(args, rank, world, local_rank):
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public ops with host tensors
+    clocks = sampler.stop()      # samples of the device-resident timed region only
     if args.no_e2e:
-        clocks = sampler.stop()
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
                               "warmup": warmup, "ms_per_step": ms_per_step, "config": {"workload": desc},
@@ -284,6 +308,7 @@ def run_ours(args, rank, world, local_rank):
     ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
     from irontensor_b200 import HostAttentionStep
     pipe = HostAttentionStep(n, S, D, Precision.BF16, causal=True, chunks=args.e2e_chunks)
+    sampler_e2e = ClockSampler(sampler.gpu_index)
 
     def step_e2e():
         pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv)
@@ -294,6 +319,7 @@ def run_ours(args, rank, world, local_rank):
             step_e2e()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler_e2e.start()
     e0.record()
     if nbh:
         for _ in range(e2e_steps):
@@ -301,7 +327,7 @@ def run_ours(args, rank, world, local_rank):
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
-    clocks = sampler.stop()      # sampled across the device-resident and the end-to-end timed regions
+    clocks_e2e = sampler_e2e.stop()
     ctx.poll_status()
     e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
     nbytes = nbh * S * D * 2
@@ -335,7 +361,7 @@ def run_ours(args, rank, world, local_rank):
                    "tflops_per_gpu": value / world, "frac_of_bf16_peak_per_gpu": value / world / peaks["bf16"]},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * nbytes,
                 "d2h_bytes_per_step": 4 * nbytes, "note": "bytes are rank 0's", "groups": args.e2e_chunks,
-                "host_cores": host_binding},
+                "host_cores": host_binding, "clocks": clocks_e2e},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roofline,
