@@ -159,19 +159,19 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
 
 // fp32 tensors with D a multiple of 4 and short to medium sequences: the latency path (the greedy
 // no-KV-cache inference pattern re-runs it once per generated token, and the reference's TINY model
-// sits at S = 256).  A CTA owns 16 consecutive query rows of one head, RW (four or two) per warp.  Keys and
+// sits at S = 256).  A CTA owns RB (16 or 32) consecutive query rows of one head, RW (two, four or eight) per warp.  Keys and
 // values stream through shared memory 32 at a time (cp.async, double buffered, rows padded by four
 // floats so that lane-per-key float4 reads are conflict free).  Scores: one key per lane, each K
 // chunk read once and used for all of the warp's rows; softmax: online, warp-reduced per tile (the
 // recurrence of src/shaders/flash_attention.metal:27-41); output: lanes over the head dimension,
 // the tile's probabilities parked in shared memory and read back four keys at a time, V read from
 // shared memory.  NJ = ceil(D / 32) output elements per lane.
-template <int NJ, int RW>
-__global__ void __launch_bounds__(32 * (16 / RW))
+template <int NJ, int RW, int RB = 16>
+__global__ void __launch_bounds__(32 * (RB / RW))
 fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                        float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
                        TensorStrides st, TensorStrides skv) {
-  constexpr int RB = 16, TK = 32, NT = 32 * (RB / RW);   // RB / RW warps, RW rows each
+  constexpr int TK = 32, NT = 32 * (RB / RW);   // RB rows per CTA: RB / RW warps, RW rows each
   extern __shared__ __align__(16) float sm[];
   const int DS = D + 4;                       // padded row stride (floats)
   float* sQ = sm;                             // [RB][D]

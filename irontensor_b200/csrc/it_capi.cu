@@ -153,6 +153,13 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
     if (D <= 32) {
       if (rw == 2) it::fa_fwd_rows_f32_kernel<1, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
       else it::fa_fwd_rows_f32_kernel<1, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
+    } else if (D <= 64 && static_cast<long long>(g16.x) * g16.y > 4LL * ctx->sm_count) {
+      // Many CTAs per SM (the reference's TINY training shape, batch 16 x 4 heads x 256 keys): the kernel is
+      // bound by its shared-memory loads, and 32-row CTAs with eight rows per warp use every K chunk and V
+      // row for twice as many rows (49 against 53 us on that shape).
+      const int smem32 = (32 * D + 4 * 32 * (D + 4) + 32 * 32) * 4;
+      const dim3 g32((S + 31) / 32, BH);
+      it::fa_fwd_rows_f32_kernel<2, 8, 32><<<g32, 128, smem32, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
     } else if (D <= 64) {
       if (rw == 2) it::fa_fwd_rows_f32_kernel<2, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
       else it::fa_fwd_rows_f32_kernel<2, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
