@@ -56,7 +56,9 @@ it_status it_stream_create(it_ctx* ctx, it_stream** out);
 /* Adopts an existing cudaStream_t (0 = the legacy default stream) without owning it. */
 it_status it_stream_wrap(it_ctx* ctx, void* cuda_stream, it_stream** out);
 it_status it_stream_destroy(it_ctx* ctx, it_stream* stream);
-/* CommandBatch::sync / ::end (src/command_batch.rs:191-226): block until the queue drains. */
+/* CommandBatch::sync / ::end (src/command_batch.rs:191-226): block until the queue drains.  Returns
+ * IT_ERR_TIMEOUT (without clearing anything) when the device status word is set, see
+ * it_attention_status_poll; so does it_event_wait. */
 it_status it_stream_sync(it_ctx* ctx, it_stream* stream);
 
 /* CommandBatch::commit_async / is_async_complete / wait_for_completion
@@ -237,9 +239,12 @@ it_status it_attention_packed_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype
  * Same arguments, results and dispatch as it_flash_attention_bwd, minus the workspace.  Differences:
  *   - the shape is refused with IT_ERR_UNSUPPORTED_SHAPE when its scratch need
  *     (it_flash_attention_bwd_workspace_bytes) exceeds IT_NOALLOC_SCRATCH_BYTES;
- *   - this call makes no cudaMalloc / cudaFree and calls nothing that allocates device memory;
+ *   - this call makes no cudaMalloc / cudaFree and calls nothing that allocates device memory; the
+ *     first call on a device may still make the CUDA runtime load this library's kernels, which is
+ *     the runtime's own one-time work -- from the second call on nothing is allocated at all;
  *   - the first call on each device looks up the array's device address (a symbol lookup, once per
- *     device): make that first call outside any stream capture;
+ *     device and process): make that first call outside any stream capture.  The address is kept for
+ *     the life of the process, so it does not survive a cudaDeviceReset by the host application;
  *   - all calls on one GPU share the one array, and it keeps the previous call's contents; the call
  *     clears what has to start from zero itself.  Two calls whose kernels can overlap on the GPU
  *     (different streams, no ordering between them) race on it: order them. */
@@ -249,11 +254,20 @@ it_status it_flash_attention_bwd_noalloc(it_ctx* ctx, it_stream* stream, it_dtyp
                                          const void* q, const void* k, const void* v, const void* o,
                                          const void* d_o, const float* lse, void* dq, void* dk, void* dv);
 
-/* Kernels never spin without bound: a wait that runs out (about one second) records a code in a
- * device status word and the kernel winds down.  This call drains `stream`, returns the word in
- * *device_status (0 = clean) and clears it.  Returns IT_ERR_TIMEOUT when the word was non-zero.
+/* Kernels never spin without bound: a wait that runs out (one second of wall-clock time on the device's
+ * global timer, which keeps counting while the context is descheduled or serialised by a tool) records a
+ * code in the context's device status word and the kernel winds down.  While the word is non-zero EVERY
+ * later launch of this library on the context, on any stream, returns at once without computing, so the
+ * outputs of those launches are not written: the C entry points still return IT_OK (they only enqueue),
+ * and it_stream_sync, it_event_wait and it_ctx_check_status report IT_ERR_TIMEOUT.
+ * it_attention_status_poll drains `stream`, returns the word in *device_status (0 = clean) and CLEARS it,
+ * after which launches compute again.  Returns IT_ERR_TIMEOUT when the word was non-zero.
  * (The reference never checks command-buffer errors; src/command_batch.rs:191-226.) */
 it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* device_status);
+/* Reads the status word without draining a caller's stream and without clearing it: IT_OK when zero,
+ * IT_ERR_TIMEOUT otherwise; *device_status (may be null) gets the word.  For hosts that synchronise by
+ * other means (their own events, a blocking copy) before they read results. */
+it_status it_ctx_check_status(it_ctx* ctx, int32_t* device_status);
 
 /* How many kernels this library has launched on this context since it was created. */
 it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out);
@@ -277,11 +291,6 @@ it_status it_ctx_kernel_ms(it_ctx* ctx, int32_t which, float* ms);
  * In every variant out = a * (b as K x N). */
 it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, const void* a_bf16,
                            const void* b_bf16, float* out);
-/* Tensor-pipe issue-rate probe: `ctas` CTAs each issue iters*8 MMAs (128 x N x 16, operands resident
- * on chip) through one operand path (0: A,B K-major smem N=128; 1: same N=256; 2: A in tensor memory,
- * B N-major, N=128; 3: A M-major, B N-major, N=128; 4: as 2 with N=256).  The caller times the launch;
- * FLOPs = ctas * iters * 8 * 2*128*N*16. */
-it_status it_selftest_umma_rate(it_ctx* ctx, it_stream* stream, int32_t variant, int32_t ctas, int32_t iters);
 /* Launches one CTA that waits `limit_ms` on a barrier nothing arrives on, so that the bounded-wait
  * path can be checked: afterwards it_attention_status_poll reports a non-zero word. */
 it_status it_selftest_wait_timeout(it_ctx* ctx, it_stream* stream, int32_t limit_ms);

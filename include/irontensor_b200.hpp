@@ -15,7 +15,9 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 #include <tuple>
@@ -54,24 +56,39 @@ inline float bf16_to_f32(uint16_t x) {
   return f;
 }
 
-// The process-wide device context and the calling thread's stream (MetalContext::global,
-// src/device.rs:27-29; the thread-local CommandBatch, src/command_batch.rs:49-53).
+// One context per device for the whole process and one stream per (thread, context) (MetalContext::global,
+// src/device.rs:27-29; the thread-local CommandBatch, src/command_batch.rs:49-53).  global() is the context of
+// the default device (0 until set_default_device); global(d) that of device d.
+// Ownership rule, as for the reference's thread-local batch: work is ordered only within the calling thread's
+// stream.  A Tensor (zeros() and uploads are enqueued, not finished, when they return) may be handed to another
+// thread only after CommandBatch::sync() on the thread that produced it.
 class Context {
  public:
-  static Context& global(int device = 0) {
-    static Context ctx(device);
-    return ctx;
+  static void set_default_device(int device) { default_device() = device; }
+  static Context& global(int device = -1) {
+    static std::mutex m;
+    static std::map<int, std::unique_ptr<Context>> all;
+    if (device < 0) device = default_device();
+    std::lock_guard<std::mutex> lock(m);
+    auto& slot = all[device];
+    if (!slot) slot.reset(new Context(device));
+    return *slot;
   }
   it_ctx* raw() const { return ctx_; }
   it_stream* stream() {
-    thread_local it_stream* s = nullptr;
+    thread_local std::map<it_ctx*, it_stream*> mine;   // streams live as long as the process, like the contexts
+    it_stream*& s = mine[ctx_];
     if (s == nullptr) check(it_stream_create(ctx_, &s));
     return s;
   }
+  ~Context() { it_ctx_destroy(ctx_); }
 
  private:
   explicit Context(int device) { check(it_ctx_create(device, &ctx_)); }
-  ~Context() { it_ctx_destroy(ctx_); }
+  static int& default_device() {
+    static int d = 0;
+    return d;
+  }
   it_ctx* ctx_ = nullptr;
 };
 
@@ -200,6 +217,18 @@ class Tensor {
 
 inline it_dtype dtype_code(Precision p) { return p == Precision::FP32 ? IT_F32 : IT_BF16; }
 
+// Scratch for the calls that need a workspace: one grow-only buffer per thread (and so per stream), reused by
+// every call, so that an op neither allocates nor drains the stream in the steady state.  Growing drains the
+// stream once before the smaller buffer is released.
+inline void* thread_workspace(size_t bytes) {
+  thread_local Tensor ws;
+  if (ws.byte_size() < bytes || ws.ptr() == nullptr) {
+    if (ws.ptr() != nullptr) check(it_stream_sync(Context::global().raw(), Context::global().stream()));
+    ws = Tensor::empty({bytes / 4 + 64}, Precision::FP32);
+  }
+  return ws.ptr();
+}
+
 // src/ops/flash_attention.rs:76-193
 inline Tensor flash_attention(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
   require(q.precision() == k.precision() && q.precision() == v.precision(), "Q, K and V must have the same precision");
@@ -241,13 +270,12 @@ inline std::tuple<Tensor, Tensor, Tensor> attention_backward_recompute(const Ten
   check(it_flash_attention_bwd_workspace_bytes(dtype_code(q.precision()), static_cast<int32_t>(s[0]),
                                                static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
                                                static_cast<int32_t>(s[3]), &ws_bytes));
-  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);   // freed after the stream has used it
+  void* const ws = thread_workspace(ws_bytes);
   check(it_flash_attention_bwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
                                static_cast<int32_t>(s[0]), static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
                                static_cast<int32_t>(s[3]), causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), o->ptr(),
                                grad_output.ptr(), static_cast<const float*>(o->lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(),
-                               ws.ptr(), ws_bytes));
-  CommandBatch::sync();   // the scratch goes out of scope here
+                               ws, ws_bytes));
   return {dq, dk, dv};
 }
 
@@ -287,12 +315,11 @@ inline std::tuple<Tensor, Tensor, Tensor> attention_backward(const Tensor& grad_
   check(it_flash_attention_bwd_workspace_bytes(dtype_code(q.precision()), static_cast<int32_t>(s[0]),
                                                static_cast<int32_t>(s[2]), static_cast<int32_t>(s[1]),
                                                static_cast<int32_t>(s[3]), &ws_bytes));
-  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  void* const ws = thread_workspace(ws_bytes);
   check(it_attention_bwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
                          static_cast<int32_t>(s[0]), static_cast<int32_t>(s[1]), static_cast<int32_t>(s[2]),
                          static_cast<int32_t>(s[3]), causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), o.ptr(), grad_output.ptr(),
-                         static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws.ptr(), ws_bytes));
-  CommandBatch::sync();   // the scratch goes out of scope here
+                         static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws, ws_bytes));
   return {dq, dk, dv};
 }
 
@@ -331,18 +358,17 @@ inline std::tuple<Tensor, Tensor, Tensor> attention_gqa_backward(const Tensor& g
   if (s[0] * s[1] * s[2] == 0) return {dq, dk, dv};
   size_t ws_bytes = 0;
   check(it_flash_attention_bwd_workspace_bytes(dtype_code(q.precision()), B, H, S, D, &ws_bytes));
-  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  void* const ws = thread_workspace(ws_bytes);
   if (rope_base > 0.f) {
     check(it_attention_gqa_bwd_rope(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()), B, S, H, Hkv,
                                     D, causal ? 1 : 0, rope_base, position_offset, q.ptr(), k.ptr(), v.ptr(), o.ptr(),
                                     grad_output.ptr(), static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(),
-                                    ws.ptr(), ws_bytes));
+                                    ws, ws_bytes));
   } else {
     check(it_attention_gqa_bwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()), B, S, H, Hkv, D,
                                causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), o.ptr(), grad_output.ptr(),
-                               static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws.ptr(), ws_bytes));
+                               static_cast<const float*>(o.lse->ptr()), dq.ptr(), dk.ptr(), dv.ptr(), ws, ws_bytes));
   }
-  CommandBatch::sync();   // the scratch goes out of scope here
   return {dq, dk, dv};
 }
 
@@ -373,11 +399,10 @@ inline Tensor attention_decode(const Tensor& q, const Tensor& k_cache, const Ten
   out.lse = std::make_shared<Tensor>(Tensor::zeros({q.shape()[0], q.shape()[1]}, Precision::FP32));
   size_t ws_bytes = 0;
   check(it_attention_decode_workspace_bytes(B, H, D, &ws_bytes));
-  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  void* const ws = thread_workspace(ws_bytes);
   check(it_attention_decode(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()), B, H, Hkv, D,
                             static_cast<int32_t>(kv_len), max_len, q.ptr(), k_cache.ptr(), v_cache.ptr(), out.ptr(),
-                            static_cast<float*>(out.lse->ptr()), ws.ptr(), ws_bytes));
-  CommandBatch::sync();
+                            static_cast<float*>(out.lse->ptr()), ws, ws_bytes));
   return out;
 }
 
@@ -418,12 +443,11 @@ inline std::tuple<Tensor, Tensor, Tensor> qkv_rope_forward(const Tensor& x, cons
          v = Tensor::empty({B, S, kv_heads, head_dim}, Precision::BF16);
   size_t ws_bytes = 0;
   check(it_qkv_rope_workspace_bytes(static_cast<int32_t>(S), static_cast<int32_t>(head_dim), &ws_bytes));
-  Tensor ws = Tensor::empty({ws_bytes / 4 + 1}, Precision::FP32);
+  void* const ws = thread_workspace(ws_bytes);
   check(it_qkv_rope_fwd(Context::global().raw(), Context::global().stream(), static_cast<int32_t>(B), static_cast<int32_t>(S),
                         static_cast<int32_t>(hidden), static_cast<int32_t>(heads), static_cast<int32_t>(kv_heads),
                         static_cast<int32_t>(head_dim), rope_base, position_offset, x.ptr(), w_qkv.ptr(), q.ptr(), k.ptr(), v.ptr(),
-                        ws.ptr(), ws_bytes));
-  CommandBatch::sync();   // the table goes out of scope here
+                        ws, ws_bytes));
   return {q, k, v};
 }
 

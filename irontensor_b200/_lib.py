@@ -34,6 +34,7 @@ SIGNATURES = {
     "it_event_record": [_vp, _vp, _vp],
     "it_event_query": [_vp, _vp, _c.POINTER(_i32)],
     "it_event_wait": [_vp, _vp],
+    "it_ctx_check_status": [_vp, _c.POINTER(_i32)],
     "it_event_elapsed_ms": [_vp, _vp, _vp, _c.POINTER(_c.c_float)],
     "it_buf_alloc": [_vp, _c.c_size_t, _c.POINTER(_vp)],
     "it_buf_free": [_vp, _vp],
@@ -67,7 +68,6 @@ SIGNATURES = {
     "it_ctx_enable_kernel_timing": [_vp, _i32],
     "it_ctx_kernel_ms": [_vp, _i32, _c.POINTER(_c.c_float)],
     "it_selftest_umma": [_vp, _vp, _i32, _vp, _vp, _vp],
-    "it_selftest_umma_rate": [_vp, _vp, _i32, _i32, _i32],
     "it_selftest_wait_timeout": [_vp, _vp, _i32],
 }
 

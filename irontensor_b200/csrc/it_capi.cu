@@ -56,6 +56,8 @@ struct it_ctx {
   int sm_count = 0;
   int* d_status = nullptr;      // device status word written by kernels whose waits run out
   int* h_status = nullptr;      // pinned mirror
+  cudaStream_t status_stream = nullptr;   // reads the status word without touching a caller's stream
+  std::mutex status_mutex;      // h_status and status_stream are shared by every thread using the context
   EncodeTiledFn encode = nullptr;
   bool timing = false;          // record events around the main kernels
   cudaEvent_t ev[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};   // [fwd|bwd][start|stop]
@@ -71,6 +73,28 @@ struct it_event {
 };
 
 namespace {
+
+// Copies the device status word to the host on the context's own stream.  Called after a caller's
+// stream or event has been waited for, so every kernel that could have written the word is done.
+it_status read_device_status(it_ctx* ctx, int* out) {
+  std::lock_guard<std::mutex> lock(ctx->status_mutex);
+  IT_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->status_stream));
+  IT_CUDA(cudaStreamSynchronize(ctx->status_stream));
+  *out = *ctx->h_status;
+  return IT_OK;
+}
+
+it_status fail_if_device_status(it_ctx* ctx) {
+  int st = 0;
+  it_status rc = read_device_status(ctx, &st);
+  if (rc != IT_OK) return rc;
+  if (st != 0)
+    return fail(IT_ERR_TIMEOUT,
+                "a bounded wait inside a kernel ran out (device status %d): results of launches since then are "
+                "invalid, and further launches on this context do nothing until it_attention_status_poll clears it",
+                st);
+  return IT_OK;
+}
 
 // A bf16 attention tensor viewed by TMA as a 4-D tensor (head_dim, seq, heads, batch) with the
 // layout's strides; one box = 128 rows x 64 columns of one (batch, head) slice, written to shared
@@ -101,11 +125,13 @@ it::TensorStrides strides_kv(bool bshd, int64_t H, int64_t Hkv, int64_t S, int64
   return t;
 }
 
-// theta_i = 1 / base^(2i / head_dim) (src/shaders/rope.metal:41-43), in double and rounded once.
+// theta_i = 1.0f / pow(base, float(2i) / float(head_dim)), every step in fp32 as the shader computes it
+// (src/shaders/rope.metal:41-43), so a CPU check that calls the same powf multiplies positions by the
+// same frequencies bit for bit.
 it::RopeFreqs make_rope_freqs(int D, float base, int position_offset, bool enabled) {
   it::RopeFreqs f;
   for (int i = 0; i < 64; ++i)
-    f.inv_freq[i] = (enabled && 2 * i < D) ? static_cast<float>(1.0 / pow(static_cast<double>(base), (2.0 * i) / D)) : 0.f;
+    f.inv_freq[i] = (enabled && 2 * i < D) ? 1.0f / powf(base, static_cast<float>(2 * i) / static_cast<float>(D)) : 0.f;
   f.enabled = enabled ? 1 : 0;
   f.position_offset = position_offset;
   return f;
@@ -131,7 +157,7 @@ bool use_sm100_path(it_dtype dtype, int32_t S, int32_t D) {
 int round_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128; }
 
 template <typename ST>
-void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
+it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
                         const void* v, void* o, float* lse, const it::TensorStrides& st, const it::TensorStrides& skv) {
   const float scale = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;   // exp2 domain
   const dim3 grid((S + 63) / 64, BH);
@@ -164,19 +190,20 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
       if (rw == 2) it::fa_fwd_rows_f32_kernel<2, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
       else it::fa_fwd_rows_f32_kernel<2, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
     } else {
-      static bool attr_set[16] = {};
+      static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
       if (!attr_set[ctx->device & 15]) {
-        cudaFuncSetAttribute(it::fa_fwd_rows_f32_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (16 * 128 + 4 * 32 * 132 + 512) * 4);
-        cudaFuncSetAttribute(it::fa_fwd_rows_f32_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (16 * 128 + 4 * 32 * 132 + 512) * 4);
+        IT_CUDA(cudaFuncSetAttribute(it::fa_fwd_rows_f32_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (16 * 128 + 4 * 32 * 132 + 512) * 4));
+        IT_CUDA(cudaFuncSetAttribute(it::fa_fwd_rows_f32_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (16 * 128 + 4 * 32 * 132 + 512) * 4));
         attr_set[ctx->device & 15] = true;
       }
       if (rw == 2) it::fa_fwd_rows_f32_kernel<4, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
       else it::fa_fwd_rows_f32_kernel<4, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
     }
     ctx->launches += 1;
-    return;
+    IT_CUDA(cudaGetLastError());
+    return IT_OK;
   }
   switch (round_dp(D)) {
     case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
@@ -185,10 +212,12 @@ void launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
     default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
   }
   ctx->launches += 1;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
 }
 
 template <typename ST>
-void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
+it_status launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
                         const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
                         float* delta, const it::TensorStrides& st, const it::TensorStrides& skv, const it::RopeFreqs& rf) {
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
@@ -202,6 +231,8 @@ void launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int c
   it::fa_bwd_generic_kernel<ST, 1><<<grid_kv, 128, 0, s>>>(qq, kk, vv, dd, lse, delta, static_cast<ST*>(dq), static_cast<ST*>(dk),
                                                            static_cast<ST*>(dv), S, D, causal, scale, st, skv, rf);
   ctx->launches += 3;
+  IT_CUDA(cudaGetLastError());
+  return IT_OK;
 }
 
 // The two tensor-core forward kernels: one query tile per CTA with the softmax groups alternating over key
@@ -220,7 +251,7 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   if ((st = make_tmap(ctx, &mq, q, B, H, S, D, sq, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mk, k, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mv, v, B, Hkv, S, D, skv, 128)) != IT_OK) return st;
-  static bool attr_set[16] = {};
+  static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
@@ -299,7 +330,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(IT_ERR_CUDA, "cuTensorMapEncodeTiled (dQ accumulator) failed with %d", static_cast<int>(r));
   }
-  static bool attr_set[16] = {};
+  static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(it::fa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
@@ -364,7 +395,7 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   const it::TensorStrides sa{lda, lda * a_rows, lda * a_rows, 1}, sb{ldb, ldb * b_rows, ldb * b_rows, 1};
   if ((st = make_tmap(ctx, &ma, a, 1, 1, a_rows, a_cols, sa, (LAYOUT == 2) ? T::BK : T::BM)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mb, b, 1, 1, b_rows, b_cols, sb, (LAYOUT == 0) ? T::BN : T::BK)) != IT_OK) return st;
-  static bool attr_set[16] = {};
+  static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(it::gemm_bf16_sm100_kernel<LAYOUT, QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  T::SMEM_BYTES));
@@ -432,7 +463,7 @@ it_status launch_decode_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv
   if ((st = make_tmap(ctx, &mk, kc, B, Hkv, kv_len, D, sc, 128)) != IT_OK) return st;
   if ((st = make_tmap(ctx, &mv, vc, B, Hkv, kv_len, D, sc, 128)) != IT_OK) return st;
   auto kernel = it::fa_fwd_pp_sm100_kernel<D, true>;
-  static bool attr_set[16] = {};
+  static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
@@ -486,7 +517,7 @@ it_status launch_decode(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv, int 
   const int pad = 16 / static_cast<int>(sizeof(ST));
   const size_t smem = static_cast<size_t>(it::DEC_GC) * D * 4 + 2ull * it::DEC_TK * (D + pad) * sizeof(ST) +
                       static_cast<size_t>(it::DEC_GC) * it::DEC_TK * 4 + 3 * it::DEC_GC * 4;
-  static bool attr_set[16] = {};
+  static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
     IT_CUDA(cudaFuncSetAttribute(it::fa_decode_split_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     attr_set[ctx->device & 15] = true;
@@ -537,7 +568,8 @@ it_status it_ctx_create(int device, it_ctx** out) {
   }
   c->encode = reinterpret_cast<EncodeTiledFn>(fn);
   if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess || cudaMemset(c->d_status, 0, sizeof(int)) != cudaSuccess ||
-      cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess) {
+      cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&c->status_stream, cudaStreamNonBlocking) != cudaSuccess) {
     delete c;
     return fail(IT_ERR_CUDA, "could not allocate the status word");
   }
@@ -550,6 +582,7 @@ it_status it_ctx_destroy(it_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
+  if (ctx->status_stream != nullptr) cudaStreamDestroy(ctx->status_stream);
   for (int a = 0; a < 2; ++a)
     for (int b = 0; b < 2; ++b)
       if (ctx->ev[a][b] != nullptr) cudaEventDestroy(ctx->ev[a][b]);
@@ -593,7 +626,7 @@ it_status it_stream_destroy(it_ctx* ctx, it_stream* stream) {
 it_status it_stream_sync(it_ctx* ctx, it_stream* stream) {
   if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
   IT_CUDA(cudaStreamSynchronize(stream->s));
-  return IT_OK;
+  return fail_if_device_status(ctx);
 }
 
 it_status it_event_create(it_ctx* ctx, it_event** out) {
@@ -640,7 +673,7 @@ it_status it_event_query(it_ctx* ctx, it_event* ev, int32_t* done) {
 it_status it_event_wait(it_ctx* ctx, it_event* ev) {
   if (ctx == nullptr || ev == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
   IT_CUDA(cudaEventSynchronize(ev->e));
-  return IT_OK;
+  return fail_if_device_status(ctx);
 }
 
 it_status it_event_elapsed_ms(it_ctx* ctx, it_event* start, it_event* stop, float* ms) {
@@ -737,12 +770,8 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
     return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
               : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
   }
-  if (dtype == IT_F32)
-    launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
-  else
-    launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
-  IT_CUDA(cudaGetLastError());
-  return IT_OK;
+  return dtype == IT_F32 ? launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv)
+                         : launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
 }
 
 it_status it_flash_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
@@ -810,12 +839,10 @@ static it_status attention_bwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
                : launch_bwd_sm100<64>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, ws, w, sv, skv, rf, sq);
   }
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
-  if (dtype == IT_F32)
-    launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv, rf);
-  else
-    launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv, rf);
-  IT_CUDA(cudaGetLastError());
-  return IT_OK;
+  return dtype == IT_F32
+             ? launch_bwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta, sv, skv, rf)
+             : launch_bwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, d_o, lse, dq, dk, dv, delta,
+                                                 sv, skv, rf);
 }
 
 it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t H, int32_t S,
@@ -1025,15 +1052,16 @@ it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_di
   it_status st = check_linear(ctx, stream, n, in_dim, out_dim);
   if (st != IT_OK) return st;
   if (in_dim == 0 || (n == 0 && out_dim == 0)) return IT_OK;
-  if (dy == nullptr || x == nullptr || w == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
-  if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || (dx && !aligned16(dx)) || (dw && !aligned16(dw)))
-    return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
-  IT_CUDA(cudaSetDevice(ctx->device));
-  if (n == 0 || out_dim == 0) {   // empty sums
+  if ((dx && !aligned16(dx)) || (dw && !aligned16(dw))) return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
+  if (n == 0 || out_dim == 0) {   // empty sums: dy and x (n == 0) or dy and w (out_dim == 0) are empty and may be null
+    IT_CUDA(cudaSetDevice(ctx->device));
     if (dx && n) IT_CUDA(cudaMemsetAsync(dx, 0, static_cast<size_t>(n) * in_dim * 2, stream->s));
     if (dw && out_dim) IT_CUDA(cudaMemsetAsync(dw, 0, static_cast<size_t>(out_dim) * in_dim * 4, stream->s));
     return IT_OK;
   }
+  if (dy == nullptr || x == nullptr || w == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(dy) || !aligned16(x) || !aligned16(w)) return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
   if (dx != nullptr &&
       (st = launch_gemm<1>(ctx, stream->s, n, in_dim, out_dim, dy, out_dim, w, in_dim, dx, in_dim, false)) != IT_OK)
     return st;
@@ -1084,15 +1112,26 @@ it_status it_flash_attention_bwd_noalloc(it_ctx* ctx, it_stream* stream, it_dtyp
 it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* device_status) {
   if (ctx == nullptr || stream == nullptr || device_status == nullptr)
     return fail(IT_ERR_INVALID_ARG, "null argument");
-  IT_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream->s));
   IT_CUDA(cudaStreamSynchronize(stream->s));
-  *device_status = *ctx->h_status;
+  int word = 0;
+  it_status rc = read_device_status(ctx, &word);
+  if (rc != IT_OK) return rc;
+  *device_status = word;
   if (*device_status != 0) {
     IT_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), stream->s));
     IT_CUDA(cudaStreamSynchronize(stream->s));
     return fail(IT_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (device status %d)", *device_status);
   }
   return IT_OK;
+}
+
+it_status it_ctx_check_status(it_ctx* ctx, int32_t* device_status) {
+  if (ctx == nullptr) return fail(IT_ERR_INVALID_ARG, "null context");
+  int word = 0;
+  it_status rc = read_device_status(ctx, &word);
+  if (rc != IT_OK) return rc;
+  if (device_status != nullptr) *device_status = word;
+  return word == 0 ? IT_OK : fail_if_device_status(ctx);
 }
 
 it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable) {
@@ -1146,30 +1185,6 @@ it_status it_selftest_umma(it_ctx* ctx, it_stream* stream, int32_t variant, cons
     IT_SELFTEST_CASE(3)
   }
 #undef IT_SELFTEST_CASE
-  ctx->launches += 1;
-  IT_CUDA(cudaGetLastError());
-  return IT_OK;
-}
-
-it_status it_selftest_umma_rate(it_ctx* ctx, it_stream* stream, int32_t variant, int32_t ctas, int32_t iters) {
-  if (ctx == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
-  if (variant < 0 || variant > 4 || ctas < 1 || ctas > 1024 || iters < 1 || iters > 100000)
-    return fail(IT_ERR_INVALID_ARG, "variant 0..4, ctas 1..1024, iters 1..100000");
-  IT_CUDA(cudaSetDevice(ctx->device));
-  const int smem = 6 * 128 * 128 + 64;
-#define IT_RATE_CASE(V)                                                                                      \
-  case V:                                                                                                    \
-    IT_CUDA(cudaFuncSetAttribute(it::umma_rate_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    it::umma_rate_kernel<V><<<ctas, 128, smem, stream->s>>>(iters, ctx->d_status);                           \
-    break;
-  switch (variant) {
-    IT_RATE_CASE(0)
-    IT_RATE_CASE(1)
-    IT_RATE_CASE(2)
-    IT_RATE_CASE(3)
-    IT_RATE_CASE(4)
-  }
-#undef IT_RATE_CASE
   ctx->launches += 1;
   IT_CUDA(cudaGetLastError());
   return IT_OK;

@@ -12,8 +12,8 @@
 // Rotating K "on load" inside the attention kernels was rejected: every K tile is loaded once per
 // query tile (S/128 times), every Q tile once per key tile in the backward, so the rotation would be
 // redone that many times on shared-memory tiles of kernels that are shared-memory bound.
-// theta_i comes from the host as a table (double precision pow, rounded once), so that any CPU
-// check can multiply the position by bit-identical frequencies.
+// theta_i comes from the host as a table computed in fp32 exactly as the shader does (powf, then one
+// division), so that a CPU check multiplies the position by bit-identical frequencies.
 #pragma once
 #include <cuda_bf16.h>
 

@@ -144,69 +144,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   }
 }
 
-// Issue-rate probe: every CTA issues `iters` x 8 back-to-back MMAs (K = 16 each) on operands that
-// already sit in shared / tensor memory, so the time of a launch is the tensor pipe's own rate for
-// that operand path.  VARIANT 0: A, B K-major smem, N=128.  1: same, N=256.  2: A from TMEM,
-// B N-major smem, N=128.  3: A M-major, B N-major smem, N=128.  4: A from TMEM, B N-major, N=256.
-template <int VARIANT>
-__global__ void __launch_bounds__(128, 1) umma_rate_kernel(int iters, int* status) {
-  using namespace ptx;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr int N = (VARIANT == 1 || VARIANT == 4) ? 256 : 128;
-  constexpr int BLOCK_BYTES = 128 * 128;
-  uint8_t* sA = smem;                       // 2 blocks: 128 rows x 128 K
-  uint8_t* sB = smem + 2 * BLOCK_BYTES;     // up to 4 blocks
-  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + 6 * BLOCK_BYTES);   // [3]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 3);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const int tid = threadIdx.x;
-  for (int i = tid; i < 6 * BLOCK_BYTES / 4; i += 128)   // small bf16 values, not all equal
-    reinterpret_cast<uint32_t*>(smem)[i] = 0x3C003C00u + ((i * 2654435761u) >> 28) * 0x00010001u;
-  if (tid == 0) {
-    *abort_flag = 0;
-    mbar_init(bar, 1);
-    mbar_init(bar + 1, 1);
-    fence_mbar_init();
-  }
-  fence_proxy_async_smem();
-  if (tid < 32) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  if (tid == 0) {
-    const uint32_t a_addr = smem_addr(sA), b_addr = smem_addr(sB);
-    constexpr uint32_t idesc = make_idesc(128, N, VARIANT == 3, VARIANT >= 2);
-    for (int it = 0; it < iters; ++it) {
-      const uint32_t d = tmem_base + (it & 1) * 256;   // two accumulators, alternating
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t koff = (kk >> 2) * BLOCK_BYTES + (kk & 3) * 32;
-        if (VARIANT == 0 || VARIANT == 1) {
-          umma_ss(d, sdesc_advance(make_sdesc(a_addr, 16, 1024), koff),
-                  sdesc_advance(make_sdesc(b_addr, 16, 1024), (kk >> 2) * (N * 128) + (kk & 3) * 32), idesc, 1);
-        } else if (VARIANT == 2 || VARIANT == 4) {
-          umma_ts(d, tmem_base + 448 + kk * 8, sdesc_advance(make_sdesc(b_addr, BLOCK_BYTES, 1024), kk * 2048), idesc, 1);
-        } else {
-          umma_ss(d, sdesc_advance(make_sdesc(a_addr, BLOCK_BYTES, 1024), kk * 2048),
-                  sdesc_advance(make_sdesc(b_addr, BLOCK_BYTES, 1024), kk * 2048), idesc, 1);
-        }
-      }
-    }
-    umma_commit(bar);
-    mbar_wait(bar, 0, abort_flag, status, DEV_ERR_TIMEOUT_MMA, 4000000000ull);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (tid < 32) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
 // Waits on a barrier that nothing ever arrives on; the wait gives up after `limit_ns`.
 __global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns) {
   __shared__ uint64_t bar;

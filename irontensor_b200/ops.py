@@ -77,6 +77,12 @@ class _Context:
         _lib.check(self.lib.it_ctx_kernel_ms(self.handle, which, ctypes.byref(ms)))
         return ms.value
 
+    def check_status(self):
+        """Raises ITError(IT_ERR_TIMEOUT) if a kernel's bounded wait ran out on this context (every later launch
+        is then a no-op and its outputs are garbage).  Does not drain a stream and does not clear the word;
+        call it after the results have been waited for.  poll_status() clears."""
+        _lib.check(self.lib.it_ctx_check_status(self.handle, None))
+
     def poll_status(self):
         """Drains the current stream; raises ITError(IT_ERR_TIMEOUT) if a kernel's wait ran out."""
         st = ctypes.c_int32()
@@ -100,7 +106,8 @@ def context(device=None):
 class CommandBatch:
     """The reference batches encoded work per thread and flushes on sync (src/command_batch.rs:167-391).
     Here work is enqueued on the thread's current CUDA stream as soon as an op is called; these
-    functions keep the same call sites meaningful."""
+    functions keep the same call sites meaningful.  sync, end and wait_for_completion raise ITError(IT_ERR_TIMEOUT)
+    when a kernel's bounded wait ran out (it_stream_sync / it_event_wait report the device status word)."""
 
     @staticmethod
     def begin():
@@ -244,12 +251,16 @@ class Tensor:
 
     def as_f32_slice(self):
         assert self._precision is Precision.FP32, "Tensor is not FP32"
-        return self._data.cpu().numpy()
+        host = self._data.cpu().numpy()      # drains the stream
+        context(self._data.device.index).check_status()   # a kernel that gave up leaves garbage here: raise instead
+        return host
 
     def as_bf16_slice(self):
         assert self._precision is Precision.BF16, "Tensor is not BF16"
         torch = _torch()
-        return self._data.view(torch.int16).cpu().numpy().view(np.uint16)
+        host = self._data.view(torch.int16).cpu().numpy().view(np.uint16)
+        context(self._data.device.index).check_status()
+        return host
 
     def to_f32_host(self):
         """Values as fp32 on the host, whatever the storage precision."""

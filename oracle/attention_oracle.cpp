@@ -15,9 +15,13 @@
 //                               attention.metal:163-207, softmax.metal:14-111,
 //                               backward/softmax.metal:22-90
 //   * bf16 rounding           : src/precision.rs:24-29
+//   * rotary embedding        : src/shaders/rope.metal:22-61, src/shaders/backward/rope.metal:25-62
+//   * repeat_kv and backward  : src/shaders/repeat_kv.metal:19-88
 // The same operation order is kept per output element (fp32, sums in index order, no FMA
 // contraction: build with -ffp-contract=off), so that on inputs both can run, this file and the
 // reference's own shader source compiled as C++ (oracle/ref_shim) agree exactly (IEEE ==).
+// The rotary embedding and repeat_kv are pinned the same way (same libm powf / cosf / sinf as the
+// compiled shader source; Apple's own pow, cos and sin cannot run here).
 // Parity status: the forward and the scalar-kernel backward composition are pinned that way; the
 // production backward's five GEMMs run in Apple's closed MPS library, whose summation order is
 // unknown, so bit-level parity with THAT is unpinned (the reference itself only asserts 1e-3 there).
@@ -311,6 +315,61 @@ int oracle_attention_bwd(int B, int H, int S, int D, int causal,
     const size_t base = (size_t)bh * S * D;
     bwd_one_head(q + base, k + base, v + base, d_o + base, dq + base, dk + base, dv + base,
                  S, D, scale, causal != 0, w0, w1, w2, t0);
+  }
+  return 0;
+}
+
+// Rotary position embedding of one [B,S,H,D] fp32 tensor (src/shaders/rope.metal:22-61), or, with
+// backward != 0, the transposed rotation of src/shaders/backward/rope.metal:25-62.  Every value is
+// computed as the shader computes it: theta = 1.0f / powf(base, float(2i) / float(D)) in fp32,
+// angle = float(position) * theta, one cosf and one sinf per element pair.
+int oracle_rope(int B, int S, int H, int D, float base, int position_offset, int backward,
+                const float* in, float* out) {
+  if (B < 0 || S < 0 || H < 0 || D < 0 || (D & 1)) return -1;   // src/ops/rope.rs:38-42
+  const int64_t rows = (int64_t)B * S * H;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const int seq_pos = (int)((r / H) % S);
+    const uint32_t position = (uint32_t)seq_pos + (uint32_t)position_offset;
+    const float* x = in + r * D;
+    float* y = out + r * D;
+    for (int pair = 0; pair < D / 2; ++pair) {
+      const float dim_idx = (float)(pair * 2);
+      const float theta = 1.0f / powf(base, dim_idx / (float)D);
+      const float angle = (float)position * theta;
+      const float c = cosf(angle), sn = sinf(angle);
+      const float x0 = x[2 * pair], x1 = x[2 * pair + 1];
+      if (backward) {
+        y[2 * pair] = x0 * c + x1 * sn;
+        y[2 * pair + 1] = -x0 * sn + x1 * c;
+      } else {
+        y[2 * pair] = x0 * c - x1 * sn;
+        y[2 * pair + 1] = x0 * sn + x1 * c;
+      }
+    }
+  }
+  return 0;
+}
+
+// repeat_kv (src/shaders/repeat_kv.metal:19-47): in [B,S,Hkv,D] -> out [B,S,H,D], output head h
+// reads head h / (H / Hkv).  backward != 0 (:49-88): in [B,S,H,D] -> out [B,S,Hkv,D], the group's
+// gradients summed in head order starting from 0.0f.
+int oracle_repeat_kv(int B, int S, int H, int Hkv, int D, int backward, const float* in, float* out) {
+  if (Hkv < 1 || H % Hkv != 0) return -1;                        // src/ops/repeat_kv.rs:77-80
+  const int rep = H / Hkv;
+  const int64_t bs = (int64_t)B * S;
+  for (int64_t t = 0; t < bs; ++t) {
+    if (backward) {
+      for (int kvh = 0; kvh < Hkv; ++kvh)
+        for (int d = 0; d < D; ++d) {
+          float sum = 0.0f;
+          for (int r = 0; r < rep; ++r) sum += in[(t * H + kvh * rep + r) * D + d];
+          out[(t * Hkv + kvh) * D + d] = sum;
+        }
+    } else {
+      for (int h = 0; h < H; ++h)
+        for (int d = 0; d < D; ++d) out[(t * H + h) * D + d] = in[(t * Hkv + h / rep) * D + d];
+    }
   }
   return 0;
 }

@@ -1,12 +1,12 @@
-"""CPU restatements (numpy) of the reference's steps either side of attention: repeat_kv and its backward,
-rotary position embedding and its backward.  TEST INFRASTRUCTURE ONLY, like attention_oracle.cpp: imported by
-tests/ (through tests/oracle_lib.py); nothing in the product loads it.
+"""Grouped-query attention as the reference composes it around its attention op (numpy): repeat_kv, attention,
+repeat_kv_backward.  TEST INFRASTRUCTURE ONLY, like attention_oracle.cpp: imported by tests/ (through
+tests/oracle_lib.py); nothing in the product loads it.
 
 Each function cites the reference shader it follows (paths relative to the reference project's root).  They take the
 attention oracle's forward / backward as arguments so that this file has no dependency of its own.
-Parity status: repeat_kv is a copy / an in-order sum and is exact; the rotary angles use Metal's pow, cos and sin in
-the reference, which cannot run here, so bit-level parity of rope is unpinned (checked against the reference's unit-test
-properties, src/ops/rope.rs:128-250, and to 1e-5 against the library)."""
+Parity status: pinned.  repeat_kv is a copy and its backward an in-order sum; tests/test_oracle.py holds gqa_expand and
+the fold below bit-for-bit to the reference's own repeat_kv shaders compiled as C++ (oracle/ref_shim) and to the
+golden vectors made from them.  The rotary embedding is restated in attention_oracle.cpp (oracle_rope)."""
 import numpy as np
 
 
@@ -39,23 +39,3 @@ def gqa_bwd(bwd, q, k, v, d_o, causal=True):
             acc += g5[:, :, r]
         return np.ascontiguousarray(acc.transpose(0, 2, 1, 3))
     return np.ascontiguousarray(dq.transpose(0, 2, 1, 3)), fold(dk), fold(dv)
-
-
-def rope(x, base=10000.0, position_offset=0, inverse=False):
-    """CPU restatement of rope_f32 / rope_backward_f32 (src/shaders/rope.metal:22-61,
-    src/shaders/backward/rope.metal:25-62) on [B,S,H,D], fp32 arithmetic: theta_i = 1 / base^(2i/D),
-    angle = float(position) * theta_i.  theta is rounded once from double, as the library's table is."""
-    x = np.asarray(x, np.float32)
-    B, S, H, D = x.shape
-    i = np.arange(D // 2)
-    theta = (1.0 / np.power(np.float64(base), (2.0 * i) / D)).astype(np.float32)
-    pos = (np.arange(S) + position_offset).astype(np.float32)
-    ang = (pos[:, None] * theta[None, :]).astype(np.float32)          # [S, D/2], the fp32 product
-    c, s = np.cos(ang).astype(np.float32)[None, :, None, :], np.sin(ang).astype(np.float32)[None, :, None, :]
-    if inverse:
-        s = -s
-    x0, x1 = x[..., 0::2], x[..., 1::2]
-    out = np.empty_like(x)
-    out[..., 0::2] = x0 * c - x1 * s
-    out[..., 1::2] = x0 * s + x1 * c
-    return out

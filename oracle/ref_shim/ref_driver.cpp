@@ -13,6 +13,11 @@
 //   ref_attention_bwd : the composition of src/train/helpers.rs:142-182 built from the scalar
 //                       kernels gemm_f32_batched, scale_f32, causal_mask_3d_f32, softmax[_fast]_f32,
 //                       softmax_backward[_fast]_f32, transpose_3d_f32.
+//   ref_rope, ref_rope_backward : rope_f32 (src/shaders/rope.metal:22-61) and rope_backward_f32
+//                       (src/shaders/backward/rope.metal:25-62) on [batch, seq, heads, head_dim],
+//                       grids as src/ops/rope.rs dispatches them (one thread per rotation pair).
+//   ref_repeat_kv, ref_repeat_kv_backward : repeat_kv_f32 / repeat_kv_backward_f32
+//                       (src/shaders/repeat_kv.metal:19-88), one thread per output element.
 #include <metal_stdlib>
 #include <cstring>
 #include <algorithm>
@@ -39,6 +44,15 @@ namespace ref_attn {
 }
 namespace ref_ew {
 #include IT_REF(src/shaders/elementwise.metal)
+}
+namespace ref_rope_f {
+#include IT_REF(src/shaders/rope.metal)
+}
+namespace ref_rope_b {
+#include IT_REF(src/shaders/backward/rope.metal)
+}
+namespace ref_rkv {
+#include IT_REF(src/shaders/repeat_kv.metal)
 }
 // The shader keywords are macros in the shim; drop them before any host code follows.
 #undef kernel
@@ -161,6 +175,38 @@ int ref_attention_bwd(int B, int H, int S, int D,
     gemm(dSt.data(), Q, tmp.data(), s, s, d);
     for (uint i = 0; i < nsd; ++i) ref_ew::scale_f32(tmp.data(), dk + bh * SD, scale, nsd, i);
   }
+  return 0;
+}
+
+int ref_rope(int B, int S, int H, int D, float base, int position_offset, int backward, const float* in,
+             float* out) {
+  if (D & 1) return -1;
+  const uint b = B, s = S, h = H, d = D;
+  if (backward) {
+    ref_rope_b::RoPEParams p{b, s, h, d, base, (uint)position_offset};
+    for (uint z = 0; z < b * h; ++z)
+      for (uint y = 0; y < s; ++y)
+        for (uint x = 0; x < d / 2; ++x) ref_rope_b::rope_backward_f32(in, out, p, uint3{x, y, z});
+  } else {
+    ref_rope_f::RoPEParams p{b, s, h, d, base, (uint)position_offset};
+    for (uint z = 0; z < b * h; ++z)
+      for (uint y = 0; y < s; ++y)
+        for (uint x = 0; x < d / 2; ++x) ref_rope_f::rope_f32(in, out, p, uint3{x, y, z});
+  }
+  return 0;
+}
+
+// forward: in [B,S,Hkv,D] -> out [B,S,H,D]; backward: in [B,S,H,D] -> out [B,S,Hkv,D]
+int ref_repeat_kv(int B, int S, int H, int Hkv, int D, int backward, const float* in, float* out) {
+  if (Hkv < 1 || H % Hkv != 0) return -1;
+  ref_rkv::RepeatKVParams p{(uint)B, (uint)S, (uint)H, (uint)Hkv, (uint)D, (uint)(H / Hkv)};
+  const uint heads_out = backward ? Hkv : H;
+  for (uint z = 0; z < (uint)(B * S); ++z)
+    for (uint y = 0; y < heads_out; ++y)
+      for (uint x = 0; x < (uint)D; ++x) {
+        if (backward) ref_rkv::repeat_kv_backward_f32(in, out, p, uint3{x, y, z});
+        else ref_rkv::repeat_kv_f32(in, out, p, uint3{x, y, z});
+      }
   return 0;
 }
 

@@ -15,7 +15,13 @@ _ref = None
 
 
 def build():
-    subprocess.run(["make", "-C", _ODIR, "-s"], check=True)
+    """Builds the oracle; the reference's shaders too when a checkout is at $IRONTENSOR_REF_ROOT or in a
+    "reference" directory beside this repository."""
+    ref = os.environ.get("IRONTENSOR_REF_ROOT") or os.path.join(os.path.dirname(_ROOT), "reference")
+    cmd = ["make", "-C", _ODIR, "-s"]
+    if os.path.isdir(os.path.join(ref, "src", "shaders")):
+        cmd.append("REF_ROOT=" + ref)
+    subprocess.run(cmd, check=True)
 
 
 def oracle():
@@ -28,6 +34,8 @@ def oracle():
         _lib.oracle_attention_fwd.argtypes = [ctypes.c_int] * 6 + [_f32p] * 5 + [ctypes.c_int] * 2
         _lib.oracle_attention_bwd.argtypes = [ctypes.c_int] * 5 + [_f32p] * 7 + [ctypes.c_int] * 2
         _lib.oracle_f32_to_bf16.argtypes = [_f32p, ctypes.POINTER(ctypes.c_uint16), ctypes.c_int64]
+        _lib.oracle_rope.argtypes = [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_int, ctypes.c_int, _f32p, _f32p]
+        _lib.oracle_repeat_kv.argtypes = [ctypes.c_int] * 6 + [_f32p, _f32p]
     return _lib
 
 
@@ -41,6 +49,8 @@ def reference():
         _ref = ctypes.CDLL(path)
         _ref.ref_attention_fwd.argtypes = [ctypes.c_int] * 6 + [_f32p] * 4
         _ref.ref_attention_bwd.argtypes = [ctypes.c_int] * 4 + [_f32p] * 7
+        _ref.ref_rope.argtypes = [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_int, ctypes.c_int, _f32p, _f32p]
+        _ref.ref_repeat_kv.argtypes = [ctypes.c_int] * 6 + [_f32p, _f32p]
     return _ref
 
 
@@ -104,13 +114,49 @@ def ref_bwd(q, k, v, d_o):
     return dq, dk, dv
 
 
-# The steps either side of attention (repeat_kv, rope) are restated in oracle/layer_oracle.py.
+def _rope_call(fn, x, base, position_offset, inverse):
+    x = _c(x)
+    B, S, H, D = x.shape
+    out = np.zeros_like(x)
+    if fn(B, S, H, D, float(base), int(position_offset), int(bool(inverse)), _p(x), _p(out)) != 0:
+        raise ValueError("head_dim must be even")
+    return out
+
+
+def rope(x, base=10000.0, position_offset=0, inverse=False):
+    """Rotary embedding of [B,S,H,D] (inverse: the backward rotation) by the C++ oracle."""
+    return _rope_call(oracle().oracle_rope, x, base, position_offset, inverse)
+
+
+def ref_rope(x, base=10000.0, position_offset=0, inverse=False):
+    """The same through the reference's own rope.metal / backward/rope.metal compiled as C++."""
+    return _rope_call(reference().ref_rope, x, base, position_offset, inverse)
+
+
+def _repeat_call(fn, x, heads, kv_heads, backward):
+    x = _c(x)
+    B, S, _, D = x.shape
+    out = np.zeros((B, S, kv_heads if backward else heads, D), np.float32)
+    if fn(B, S, heads, kv_heads, D, int(backward), _p(x), _p(out)) != 0:
+        raise ValueError("num_heads must be divisible by num_kv_heads")
+    return out
+
+
+def repeat_kv(x, heads, backward=False, kv_heads=None):
+    """repeat_kv ([B,S,Hkv,D] -> [B,S,H,D]) or its backward ([B,S,H,D] -> [B,S,Hkv,D]) by the C++ oracle."""
+    return _repeat_call(oracle().oracle_repeat_kv, x, heads, kv_heads if backward else x.shape[2], backward)
+
+
+def ref_repeat_kv(x, heads, backward=False, kv_heads=None):
+    return _repeat_call(reference().ref_repeat_kv, x, heads, kv_heads if backward else x.shape[2], backward)
+
+
+# Grouped-query attention as the reference composes it is restated in oracle/layer_oracle.py.
 import importlib.util as _ilu
 _spec = _ilu.spec_from_file_location("layer_oracle", os.path.join(_ODIR, "layer_oracle.py"))
 _layer = _ilu.module_from_spec(_spec)
 _spec.loader.exec_module(_layer)
 gqa_expand = _layer.gqa_expand
-rope = _layer.rope
 
 
 def gqa_fwd(q, k, v, causal=True):

@@ -3,16 +3,14 @@ vectors produced by the reference's own shader sources.
 
 Tolerances
   fp32 tensors : max-abs <= 1e-4 on O, LSE, dQ, dK, dV (as stated for the path).
-  bf16 tensors : max-abs <= 2e-2 against the fp32 oracle (as stated for the path).
-                 Relative L2: the stated bound is 1e-3, which no bf16 result can meet against an
-                 fp32 oracle -- rounding the oracle's OWN output to bf16 already gives 1.5e-3..1.7e-3
-                 (returned by gpu_util.err_stats as `floor`).  On top of that floor the kernels add
-                 what every bf16 tensor-core attention adds: P and dS are rounded to bf16 (2^-9
-                 relative) before their MMAs (the hardware rejects an fp16 A operand next to a bf16 B
-                 operand, so a wider format is not available at full rate).  Measured: O 1.9e-3..2.3e-3,
-                 dV 2.2e-3..2.4e-3, dQ/dK 2.9e-3..3.1e-3 raw.  The tests therefore bound the raw figure
-                 by 3.5e-3 and the part beyond the storage floor (removed in quadrature) by 3e-3,
-                 and report both; LSE, which stays fp32, is held to 1e-4.
+  bf16 tensors : max-abs <= 2e-2 against the fp32 oracle (as stated for the path); LSE, which stays fp32, 1e-4.
+                 Relative L2: the stated 1e-3 is unattainable for a result STORED in bf16 -- rounding the oracle's own
+                 output to bf16 gives 1.48e-3 for a uniform mantissa ((2^-8/sqrt(3))/sqrt(7/3)), 1.5e-3..1.7e-3 on these
+                 data (gpu_util.err_stats returns it as `floor`).  On top of the floor the kernels add what every bf16
+                 tensor-core attention adds: P and dS are rounded to bf16 (2^-9 relative) before their MMAs, and dS
+                 carries P's rounding as well.  The bounds are per tensor, about 10 % above the worst value measured
+                 over every bf16 case of this file (BF16_REL_L2), so that a regression of any one tensor shows.
+                 With IT_ERR_STATS_FILE set, the worst figures of the run are written there as JSON.
 """
 import ctypes
 import math
@@ -30,8 +28,9 @@ pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 F32_TOL = 1e-4
 BF16_MAX_ABS = 2e-2
-BF16_REL_L2 = 3e-3
-BF16_REL_L2_RAW = 3.5e-3
+# raw relative-L2 bound per tensor (measured worst: O 2.3e-3, dV 2.4e-3, dQ and dK 3.1e-3)
+BF16_REL_L2 = {"O": 2.5e-3, "dV": 2.6e-3, "dQ": 3.4e-3, "dK": 3.4e-3}
+_worst = {}
 
 
 def seeded(seed, B, H, S, D, bf16=False, qk_scale=1.0):
@@ -44,13 +43,21 @@ def check_f32(got, want, name):
     assert err <= F32_TOL, f"{name}: max-abs {err:.3e} > {F32_TOL}"
 
 
-def check_bf16(got, want, name):
+def check_bf16(got, want, name, rel_scale=1.0):
+    """`name` ends in the tensor's kind (O, dQ, dK, dV), which selects the relative-L2 bound."""
     assert not np.isnan(got).any(), f"{name}: NaN in output"
+    kind = name.split()[-1]
     mx, rel, floor = gu.err_stats(got, want)
     own = math.sqrt(max(rel * rel - floor * floor, 0.0))
+    w = _worst.setdefault(kind, {"max_abs": 0.0, "rel_l2": 0.0, "rel_l2_beyond_floor": 0.0})
+    w["max_abs"], w["rel_l2"], w["rel_l2_beyond_floor"] = max(w["max_abs"], mx), max(w["rel_l2"], rel), max(w["rel_l2_beyond_floor"], own)
+    if os.environ.get("IT_ERR_STATS_FILE"):
+        import json
+        with open(os.environ["IT_ERR_STATS_FILE"], "w") as f:
+            json.dump(_worst, f)
     assert mx <= BF16_MAX_ABS, f"{name}: max-abs {mx:.3e} > {BF16_MAX_ABS}"
-    assert own <= BF16_REL_L2, f"{name}: rel-L2 beyond the bf16 storage floor {own:.3e} > {BF16_REL_L2} (raw {rel:.3e}, floor {floor:.3e})"
-    assert rel <= BF16_REL_L2_RAW, f"{name}: raw rel-L2 {rel:.3e}"
+    bound = BF16_REL_L2[kind] * rel_scale
+    assert rel <= bound, f"{name}: rel-L2 {rel:.3e} > {bound:.1e} (bf16 storage floor {floor:.3e}, beyond it {own:.3e})"
 
 
 # ---------------------------------------------------------------- hardware self tests
@@ -70,7 +77,28 @@ def test_umma_operand_paths(it_ctx, variant):
 
 
 def test_bounded_wait_reports_timeout(it_ctx):
+    """A wait that runs out (a 20 ms wait on a barrier nothing arrives on: nothing faults) sets the status word.
+    Until it is cleared every host-side drain reports it -- it_stream_sync, it_ctx_check_status, CommandBatch.sync,
+    Tensor.as_*_slice -- and launches do nothing, so a host layer can never hand out the garbage silently."""
+    import torch
+    from irontensor_b200 import CommandBatch, Precision, Tensor, flash_attention
+    from irontensor_b200._lib import ITError
     _lib.check(it_ctx.lib.it_selftest_wait_timeout(it_ctx.handle, it_ctx.stream(), 20))
+    assert it_ctx.lib.it_stream_sync(it_ctx.handle, it_ctx.stream()) == _lib.IT_ERR_TIMEOUT
+    word = ctypes.c_int32()
+    assert it_ctx.lib.it_ctx_check_status(it_ctx.handle, ctypes.byref(word)) == _lib.IT_ERR_TIMEOUT and word.value == 6
+    with pytest.raises(ITError):
+        CommandBatch.sync()
+    # a launch while the word is set returns at once: its output keeps the poison, and reading it raises
+    x = Tensor.from_f32_as_bf16(np.ones(128 * 64, np.float32), [1, 1, 128, 64])
+    out = flash_attention(x, x, x, True)
+    out._data.fill_(float("nan"))
+    raw.fwd(_lib.IT_BF16, 1, 1, 128, 64, True, x.data_ptr(), x.data_ptr(), x.data_ptr(), out.data_ptr(), out.lse.data_ptr(),
+            ctx=it_ctx)
+    torch.cuda.synchronize()
+    assert torch.isnan(out._data.float()).all()
+    with pytest.raises(ITError):
+        out.as_bf16_slice()
     st = ctypes.c_int32()
     rc = it_ctx.lib.it_attention_status_poll(it_ctx.handle, it_ctx.stream(), ctypes.byref(st))
     assert rc == _lib.IT_ERR_TIMEOUT and st.value == 6
@@ -218,13 +246,16 @@ def _full_size_slices(it_ctx, B, H, S, D, seed, qk_scale, slices):
 
 
 def test_config3_gpt_small_width_bf16(it_ctx):
-    _full_size_slices(it_ctx, 32, 12, 1024, 64, synth.BASE_SEED + 3, 1.0, slices=[0, 191, 383])
+    # slices on both sides of the boundaries of the CTA order's groups of four, spread over the 384, and the tail
+    _full_size_slices(it_ctx, 32, 12, 1024, 64, synth.BASE_SEED + 3, 1.0, slices=[0, 3, 4, 97, 191, 192, 290, 376, 383])
 
 
 def test_config4_long_context_bf16(it_ctx):
     import torch
     B, H, S, D = 4, 16, 8192, 128
-    tq, tk, tv, tdo, o, lse, g = _full_size_slices(it_ctx, B, H, S, D, synth.BASE_SEED + 4, 0.5, slices=[63])
+    # Slices either side of a boundary of the backward's groups of four (3 | 4), inside the forward's tail group of
+    # eight (56, 63), and in the middle: an index slip in the CTA -> (slice, tile) maps would hit some and not others.
+    tq, tk, tv, tdo, o, lse, g = _full_size_slices(it_ctx, B, H, S, D, synth.BASE_SEED + 4, 0.5, slices=[0, 3, 4, 31, 56, 63])
     # size-independent properties on the whole tensor ------------------------------------------
     # (1) the shard of a contiguous (batch*head) range equals the same range of the full run, bit for bit
     b0, b1 = 16, 24
@@ -234,6 +265,18 @@ def test_config4_long_context_bf16(it_ctx):
             o2.data_ptr(), lse2.data_ptr(), ctx=it_ctx)
     assert it_ctx.poll_status() == 0
     assert torch.equal(o2, o[b0:b1]) and torch.equal(lse2, lse[b0:b1])
+    # ... and so does the backward of an 8-slice shard (the launch one of eight GPUs runs): dK and dV bit for bit,
+    # dQ (summed by reduce-adds in arrival order) within the bf16 tolerance
+    g2 = [torch.full_like(o2, float("nan")) for _ in range(3)]
+    n2 = raw.bwd_workspace_bytes(_lib.IT_BF16, 1, b1 - b0, S, D)
+    ws2 = torch.empty(n2, dtype=torch.uint8, device="cuda")
+    raw.bwd(_lib.IT_BF16, 1, b1 - b0, S, D, True, tq[b0:b1].data_ptr(), tk[b0:b1].data_ptr(), tv[b0:b1].data_ptr(),
+            o2.data_ptr(), tdo[b0:b1].data_ptr(), lse2.data_ptr(), g2[0].data_ptr(), g2[1].data_ptr(), g2[2].data_ptr(),
+            ws2.data_ptr(), n2, ctx=it_ctx)
+    assert it_ctx.poll_status() == 0
+    assert torch.equal(g2[1], g[1][b0:b1]) and torch.equal(g2[2], g[2][b0:b1])
+    assert (g2[0].float() - g[0][b0:b1].float()).abs().max().item() <= BF16_MAX_ABS
+    del g2, ws2
     # (2) O is linear in V: doubling V doubles O exactly (a power of two commutes with rounding)
     v2 = (tv[b0:b1].float() * 2).to(torch.bfloat16)
     o3 = torch.empty_like(o2)
@@ -342,6 +385,17 @@ def test_error_codes(it_ctx):
     assert lib.it_flash_attention_bwd(*args, ws, n - 1) == _lib.IT_ERR_INVALID_ARG
     assert lib.it_flash_attention_bwd(*args, None, n) == _lib.IT_ERR_INVALID_ARG
     assert lib.it_flash_attention_bwd(*args, ws + 16, n) == _lib.IT_ERR_ALIGNMENT
+    # linear_backward with no rows: dy [0,out] and x [0,in] are empty (null from a C caller), dW is a sum over nothing
+    dw = torch.full((16, 8), float("nan"), device="cuda")
+    assert lib.it_linear_bwd(h, s, 0, 8, 16, None, None, p, None, dw.data_ptr()) == _lib.IT_OK
+    torch.cuda.synchronize()
+    assert torch.equal(dw, torch.zeros_like(dw))
+    # ... and with no output features: dx [n,in] is a sum over nothing, w [0,in] and dy [n,0] may be null
+    dx = torch.full((4, 8), 1.0, dtype=torch.bfloat16, device="cuda")
+    assert lib.it_linear_bwd(h, s, 4, 8, 0, None, p, None, dx.data_ptr(), None) == _lib.IT_OK
+    torch.cuda.synchronize()
+    assert torch.equal(dx, torch.zeros_like(dx))
+    assert lib.it_linear_bwd(h, s, 4, 8, 16, None, p, p, dx.data_ptr(), None) == _lib.IT_ERR_INVALID_ARG
     assert it_ctx.poll_status() == 0
 
 

@@ -211,3 +211,65 @@ def test_rope_oracle_against_reference_unit_values():
         assert abs(r[0, p, 0, 0] - math.cos(p)) < 1e-6 and abs(r[0, p, 0, 1] - math.sin(p)) < 1e-6
     # position offset shifts the angle
     assert np.allclose(ol.rope(e, position_offset=2)[0, 0, 0, :2], [math.cos(2), math.sin(2)], atol=1e-6)
+
+
+# ---------------------------------------------------------------- rotary embedding and repeat_kv: pinned
+def test_golden_rope_vectors():
+    """oracle_rope against the outputs of the reference's rope_f32 / rope_backward_f32 (compiled as C++) on the inputs
+    of the reference's own tests (src/ops/rope.rs:128-250) and at positions near 8192: bit for bit, since both call
+    the same libm powf, cosf and sinf in the same order."""
+    g = gold("rope_kat")
+    assert np.array_equal(ol.rope(g["simple_in"]), g["simple_out"])
+    assert np.array_equal(ol.rope(g["zero_in"]), g["zero_out"])
+    assert np.array_equal(g["zero_out"], g["zero_in"])                       # test_rope_position_zero
+    assert np.array_equal(ol.rope(g["larger_in"]), g["larger_out"])
+    assert np.array_equal(ol.rope(g["larger_out"], inverse=True), g["larger_back"])
+    assert np.abs(g["larger_back"] - g["larger_in"]).max() < 1e-6            # backward undoes forward
+    assert np.array_equal(ol.rope(g["offset_in"], position_offset=10), g["offset_out"])
+    assert np.array_equal(ol.rope(g["long_in"], position_offset=8188), g["long_out"])
+
+
+def test_golden_repeat_kv_vectors():
+    """oracle_repeat_kv and the numpy forms the grouped-query oracle uses (gqa_expand, the in-order fold) against the
+    outputs of the reference's repeat_kv_f32 / repeat_kv_backward_f32 on its own test inputs
+    (src/ops/repeat_kv.rs:308-440): bit for bit."""
+    g = gold("repeat_kv_kat")
+    assert np.array_equal(ol.repeat_kv(g["simple_in"], 8), g["simple_out"])
+    assert np.array_equal(ol.gqa_expand(g["simple_in"], 8), g["simple_out"])
+    assert np.array_equal(ol.repeat_kv(g["backward_in"], 8, backward=True, kv_heads=2), g["backward_out"])
+    assert np.array_equal(ol.repeat_kv(g["norepeat_in"], 4), g["norepeat_out"])
+    assert np.array_equal(g["norepeat_out"], g["norepeat_in"])
+    mid = ol.repeat_kv(g["roundtrip_in"], 4)
+    assert np.array_equal(mid, g["roundtrip_mid"])
+    assert np.array_equal(ol.repeat_kv(mid, 4, backward=True, kv_heads=2), g["roundtrip_out"])
+    assert np.array_equal(g["roundtrip_out"], 2 * g["roundtrip_in"])          # each head was repeated twice
+
+
+def test_gqa_fold_equals_repeat_kv_backward():
+    """The group sum inside the grouped-query oracle (oracle/layer_oracle.py:gqa_bwd) is the reference's
+    repeat_kv_backward: same summation order, so equal bits on random data."""
+    rng = np.random.default_rng(9)
+    B, S, H, Hkv, D = 2, 5, 6, 2, 8
+    g = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    want = ol.repeat_kv(g, H, backward=True, kv_heads=Hkv)
+    acc = np.zeros((B, S, Hkv, D), np.float32)
+    g5 = g.reshape(B, S, Hkv, H // Hkv, D)
+    for r in range(H // Hkv):
+        acc += g5[:, :, :, r]
+    assert np.array_equal(acc, want)
+
+
+@pytest.mark.skipif(ol.reference() is None, reason="oracle/_ref not built (needs the reference tree)")
+def test_rope_and_repeat_kv_equal_the_compiled_reference_shaders():
+    rng = np.random.default_rng(21)
+    for (B, S, H, D, off) in [(1, 3, 2, 4, 0), (2, 33, 3, 64, 7), (1, 17, 2, 128, 8000), (1, 5, 1, 2, 0)]:
+        x = rng.standard_normal((B, S, H, D)).astype(np.float32)
+        for base in (10000.0, 500000.0):
+            assert np.array_equal(ol.rope(x, base, off), ol.ref_rope(x, base, off))
+            assert np.array_equal(ol.rope(x, base, off, inverse=True), ol.ref_rope(x, base, off, inverse=True))
+    for (B, S, H, Hkv, D) in [(1, 2, 4, 1, 8), (2, 3, 6, 3, 5), (1, 4, 8, 8, 16)]:
+        x = rng.standard_normal((B, S, Hkv, D)).astype(np.float32)
+        assert np.array_equal(ol.repeat_kv(x, H), ol.ref_repeat_kv(x, H))
+        gx = rng.standard_normal((B, S, H, D)).astype(np.float32)
+        assert np.array_equal(ol.repeat_kv(gx, H, backward=True, kv_heads=Hkv),
+                              ol.ref_repeat_kv(gx, H, backward=True, kv_heads=Hkv))
