@@ -178,6 +178,44 @@ def cpu_oracle_rate(S, D, qk_scale, n_slices, seed):
     return (flops_fwd(n_slices, S, D) + flops_bwd(n_slices, S, D)) / dt / 1e12, dt, cores
 
 
+def oracle_on_slices(q, k, v, d_o):
+    """Runs the CPU oracle (forward + composed backward, all host threads) on host arrays [n, S, D] of
+    bf16-representable fp32.  Returns (o, lse, dq, dk, dv, seconds, threads)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    ol.oracle().oracle_set_num_threads(os.cpu_count() or 1)   # torchrun sets OMP_NUM_THREADS=1
+    ol.fwd(q[None, :1, :256], k[None, :1, :256], v[None, :1, :256])   # load the library, warm the thread pool
+    t0 = time.perf_counter()
+    o, lse = ol.fwd(q[None], k[None], v[None], True)
+    dq, dk, dv = ol.bwd(q[None], k[None], v[None], d_o[None], True)
+    dt = time.perf_counter() - t0
+    return o[0], lse[0], dq[0], dk[0], dv[0], dt, ol.oracle().oracle_num_threads()
+
+
+def parity_against_oracle(slices, dev, S, D):
+    """Compares what the device-resident run left in HBM with the CPU oracle on the same inputs, for the listed
+    (batch x head) slices.  `dev` = (q, k, v, d_o, o, lse, dq, dk, dv) torch tensors [n, S, D] / [n, S].
+    Returns the `parity` dict of the JSON line and the oracle's rate for the `cpu_baseline` dict."""
+    import numpy as np
+    import torch
+    idx = torch.tensor(slices, device=dev[0].device)
+    host = [t.index_select(0, idx).float().cpu().numpy() for t in dev]
+    q, k, v, d_o, o, lse, dq, dk, dv = host
+    ro, rlse, rdq, rdk, rdv, dt, threads = oracle_on_slices(q, k, v, d_o)
+    out = {"slices": list(slices), "against": "CPU oracle (oracle/attention_oracle.cpp) on the same inputs, fp32",
+           "max_abs": {}, "rel_l2": {}, "lse_max_abs": float(np.abs(lse - rlse).max()),
+           "tolerance": {"max_abs": 2e-2, "lse_max_abs": 1e-4,
+                         "rel_l2": "1e-3 stated; a bf16-stored result cannot be below 1.48e-3 against an fp32 oracle"}}
+    for name, got, want in (("O", o, ro), ("dQ", dq, rdq), ("dK", dk, rdk), ("dV", dv, rdv)):
+        g64, w64 = got.astype(np.float64), want.astype(np.float64)
+        out["max_abs"][name] = float(np.abs(g64 - w64).max())
+        out["rel_l2"][name] = float(np.linalg.norm(g64 - w64) / (np.linalg.norm(w64) + 1e-300))
+    out["within_max_abs"] = bool(max(out["max_abs"].values()) <= 2e-2 and out["lse_max_abs"] <= 1e-4)
+    n = len(slices)
+    rate = (flops_fwd(n, S, D) + flops_bwd(n, S, D)) / dt / 1e12
+    return out, rate, dt, threads
+
+
 def run_reference(args, rank, world):
     """The reference's algorithm on the host cores (the CPU oracle, all threads)."""
     if rank != 0:
@@ -315,8 +353,8 @@ def run_ours(args, rank, world, local_rank):
     pipe = HostAttentionStep(n, S, D, Precision.BF16, causal=True, chunks=args.e2e_chunks)
     sampler_e2e = ClockSampler(sampler.gpu_index)
 
-    def step_e2e():
-        pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv)
+    def step_e2e(copies_only=False):
+        pipe.run(hq, hk, hv, hdo, ho, hdq, hdk, hdv, copies_only=copies_only)
 
     e2e_steps = steps
     if nbh:
@@ -326,14 +364,31 @@ def run_ours(args, rank, world, local_rank):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler_e2e.start()
     e0.record()
+    issue_s = 0.0
     if nbh:
         for _ in range(e2e_steps):
+            t_issue = time.perf_counter()
             step_e2e()
+            issue_s += time.perf_counter() - t_issue     # host time spent enqueueing (the call does not wait for the GPU)
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
     clocks_e2e = sampler_e2e.stop()
     ctx.poll_status()
+    host_issue_ms = max_over_ranks(issue_s / e2e_steps * 1e3)
+    # the same uploads and downloads, same groups, streams and pinned buffers, without the kernels
+    ho_keep = ho.clone() if nbh else None
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    if nbh:
+        for _ in range(e2e_steps):
+            step_e2e(copies_only=True)
+    c1.record()
+    barrier()
+    copy_only_ms = max_over_ranks(c0.elapsed_time(c1) / e2e_steps)
+    if nbh:
+        ho.copy_(ho_keep)
     e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
     nbytes = nbh * S * D * 2
     if nbh:
@@ -366,6 +421,10 @@ def run_ours(args, rank, world, local_rank):
                    "tflops_per_gpu": value / world, "frac_of_bf16_peak_per_gpu": value / world / peaks["bf16"]},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * nbytes,
                 "d2h_bytes_per_step": 4 * nbytes, "note": "bytes are rank 0's", "groups": args.e2e_chunks,
+                "copy_only_ms": copy_only_ms, "host_issue_ms": host_issue_ms,
+                "copy_only_gbs_per_direction": 4 * nbytes / (copy_only_ms * 1e-3) / 1e9 if nbh else None,
+                "breakdown_note": "copy_only_ms: the step's uploads and downloads alone on the same streams; host_issue_ms: "
+                                  "wall time the host spends enqueueing one step; both max over ranks",
                 "host_cores": host_binding, "clocks": clocks_e2e},
         "gpu_launches": int(launches),
         "clocks": clocks,
@@ -373,17 +432,198 @@ def run_ours(args, rank, world, local_rank):
     }
     if world == 1 and not args.no_cpu:
         os.sched_setaffinity(0, all_cores)   # the CPU baseline uses every core the process was given
-        n_slices = 4 if S >= 4096 else min(BH, 32)
-        r, dt, cores = cpu_oracle_rate(S, D, qs, n_slices, 0x1A7E5EED + 4)
+        # The oracle runs on the very slices the GPU just processed (inputs and results downloaded from HBM): slices either
+        # side of a boundary of the backward's CTA-order groups of four (3 | 4), the first and the last (the forward's tail
+        # group).  One run gives both the parity figures and the CPU baseline's time.
+        want = [0, 3, 4, BH - 1] if S >= 4096 else sorted(set([0, 3, 4, BH // 2, BH - 1] + list(range(8, min(BH, 35)))))
+        sl = [b for b in sorted(set(want)) if 0 <= b < nbh]
+        step_device()                         # results of the device-resident path (the e2e leg shares no buffers with it)
+        ctx.poll_status()
+        parity, r, dt, cores = parity_against_oracle(sl, (q, k, v, d_o, o, lse, dq, dk, dv), S, D)
+        line["parity"] = parity
         line["cpu_baseline"] = {"value": r, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                "sample": f"{n_slices} of {BH} (batch x head) slices at full S={S}, fwd+bwd, {dt:.1f} s"}
+                                "sample": f"{len(sl)} of {BH} (batch x head) slices at full S={S} (the slices of `parity`), "
+                                          f"fwd+bwd, {dt:.1f} s"}
+    if world == 1 and args.workload == "c4" and not args.no_secondary:
+        line["secondary"] = secondary_configs(ctx, peaks)
     print(json.dumps(line), flush=True)
 
 
+def _timed_us(fn, reps, flush):
+    """Median and minimum device time of fn() in microseconds (CUDA events); `flush`: a buffer larger than L2
+    written before each call, or None to leave L2 warm."""
+    import torch
+    ts = []
+    for i in range(reps):
+        if flush is not None:
+            flush.fill_(i & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(ts), min(ts)
+
+
+def measure_c1(ctx, peaks, flush, steps, warmup):
+    """fp32 causal forward B16 H4 S256 D64 (the reference's own benchmark shape), device-resident."""
+    import torch
+    from irontensor_b200 import _lib, raw
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x1A7E5EED + 1)
+    B, H, S, D = 16, 4, 256, 64
+    q, k, v = (torch.randn((B, H, S, D), generator=gen, device="cuda") for _ in range(3))
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, S), device="cuda")
+
+    def f():
+        raw.fwd(_lib.IT_F32, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
+    for _ in range(max(warmup, 3)):
+        f()
+    med_cold, min_cold = _timed_us(f, steps, flush)
+    med_warm, min_warm = _timed_us(f, steps, None)
+    flops, nbytes = 2.0 * B * H * S * S * D, 4 * B * H * S * D * 4 + B * H * S * 4
+    return {"metric": "causal attention forward latency", "unit": "us", "value": med_cold, "higher_is_better": False,
+            "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "causal fp32 attention forward B16 H4 S256 D64", "l2": "flushed between calls (value); warm figures alongside"},
+            "us_min": min_cold, "us_warm_l2": med_warm, "gbs": nbytes / med_cold / 1e3, "gbs_warm_l2": nbytes / med_warm / 1e3,
+            "tflops": flops / med_cold / 1e6, "roofline": {"bound": "hbm", "achieved": nbytes / med_cold / 1e3, "peak": peaks["hbm"],
+                                                           "unit": "GB/s", "frac": nbytes / med_cold / 1e3 / peaks["hbm"], "traffic": None}}
+
+
+def measure_c5(ctx, peaks, steps, warmup):
+    """The greedy no-KV-cache pattern: fp32 causal forward B1 H4 D64 at every prefix length 20..119 (100 calls),
+    eager, replayed from one CUDA graph, and served from a key/value cache instead."""
+    import torch
+    from irontensor_b200 import _lib, raw
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x1A7E5EED + 5)
+    H, D = 4, 64
+    lens = list(range(20, 120))
+    bufs = []
+    for S in lens:
+        q, k, v = (torch.randn((1, H, S, D), generator=gen, device="cuda") for _ in range(3))
+        bufs.append((S, q, k, v, torch.empty_like(q), torch.empty((1, H, S), device="cuda")))
+
+    def seq():
+        for S, q, k, v, o, lse in bufs:
+            raw.fwd(_lib.IT_F32, 1, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
+    for _ in range(max(warmup, 3)):
+        seq()
+    torch.cuda.synchronize()
+    med_eager, min_eager = _timed_us(seq, steps, None)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        seq()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            seq()
+    torch.cuda.synchronize()
+    med_graph, min_graph = _timed_us(graph.replay, steps, None)
+    # The same generation served from a key/value cache (it_attention_decode): each step attends one new token
+    # against the cached positions instead of recomputing the whole prefix.
+    kc = torch.randn((1, 128, H, D), generator=gen, device="cuda")
+    vc = torch.randn((1, 128, H, D), generator=gen, device="cuda")
+    qd = torch.randn((1, H, D), generator=gen, device="cuda")
+    od = torch.empty_like(qd)
+    nws = raw.decode_workspace_bytes(1, H, D)
+    wsd = torch.empty(nws, dtype=torch.uint8, device="cuda")
+
+    def seq_cached():
+        for S in lens:
+            raw.decode(_lib.IT_F32, 1, H, H, D, S, 128, qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), od.data_ptr(), None,
+                       wsd.data_ptr(), nws, ctx=ctx)
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        seq_cached()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph2, stream=side):
+            seq_cached()
+    torch.cuda.synchronize()
+    med_cached, _ = _timed_us(graph2.replay, steps, None)
+    flops = sum(512.0 * S * S for S in lens)
+    nbytes = sum(4112.0 * S for S in lens)
+    line = {"metric": "greedy no-KV-cache attention forward, per-call latency", "unit": "us", "value": med_graph / len(lens),
+            "higher_is_better": False, "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "dtype": "f32",
+            "data": "synthetic", "config": {"workload": "fp32 causal forward B1 H4 D64 at prefix lengths 20..119 (100 calls)",
+                                            "note": "value = one CUDA-graph replay of the 100 calls / 100; tensors stay in L2 (28.6 MB in total)"},
+            "us_per_call_eager": med_eager / len(lens), "us_per_call_graph_min": min_graph / len(lens),
+            "us_per_call_with_kv_cache": med_cached / len(lens),
+            "gbs": nbytes / med_graph / 1e3, "tflops": flops / med_graph / 1e6,
+            "roofline": {"bound": "hbm", "achieved": nbytes / med_graph / 1e3, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": nbytes / med_graph / 1e3 / peaks["hbm"], "traffic": None,
+                         "note": "launch-latency bound: the HBM time of the longest call is 0.08 us"}}
+    return line
+
+
+
+
+def measure_fwd_bwd(ctx, peaks, flush, workload, steps, warmup):
+    """bf16 causal forward + backward of one of WORKLOADS, device-resident, one GPU: ms per step and TFLOP/s."""
+    import torch
+    from irontensor_b200 import _lib, raw
+    B, H, S, D, qs, desc = WORKLOADS[workload]
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x1A7E5EED + int(workload[1:]))
+    mk = lambda sc: (torch.randn((B * H, S, D), generator=gen, device="cuda") * sc).to(torch.bfloat16)
+    q, k, v, d_o = mk(qs), mk(qs), mk(1.0), mk(1.0)
+    o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    lse = torch.empty((B * H, S), device="cuda")
+    nws = raw.bwd_workspace_bytes(_lib.IT_BF16, B, H, S, D)
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda")
+
+    def f():
+        raw.fwd(_lib.IT_BF16, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
+        raw.bwd(_lib.IT_BF16, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+                lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), nws, ctx=ctx)
+    for _ in range(max(warmup, 3)):
+        f()
+    med, mn = _timed_us(f, steps, flush)
+    flops = flops_fwd(B * H, S, D) + flops_bwd(B * H, S, D)
+    return {"workload": desc, "ms_per_step": med / 1e3, "ms_min": mn / 1e3, "tflops": flops / med / 1e6,
+            "frac_of_bf16_peak": flops / med / 1e6 / peaks["bf16"], "steps": steps, "l2": "flushed between steps"}
+
+
+def secondary_configs(ctx, peaks):
+    """Short single-GPU reports on the four configurations that are not the headline one, each with its own clock
+    sample: C1 (fp32 forward latency and achieved HBM rate), C2 and C3 (bf16 forward + backward), C5 (per-call
+    latency of the 100-call greedy pattern in a CUDA graph)."""
+    import torch
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    gpu = torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else \
+        os.environ["CUDA_VISIBLE_DEVICES"].split(",")[torch.cuda.current_device()]
+    out = {}
+
+    def sampled(name, fn):
+        sm = ClockSampler(gpu)
+        sm.start()
+        time.sleep(0.15)     # nvidia-smi needs a moment to deliver its first sample
+        sm.mark()
+        r = fn()             # each measurement warms up by itself; the samples cover its warm-up too
+        r["clocks"] = sm.stop()
+        out[name] = r
+
+    def c1():
+        m = measure_c1(ctx, peaks, flush, 200, 3)
+        return {"workload": m["config"]["workload"], "us": m["value"], "us_warm_l2": m["us_warm_l2"], "gbs": m["gbs"],
+                "frac_of_hbm_peak": m["roofline"]["frac"], "tflops": m["tflops"]}
+
+    def c5():
+        m = measure_c5(ctx, peaks, 20, 3)
+        return {"workload": m["config"]["workload"], "us_per_call_graph": m["value"], "us_per_call_eager": m["us_per_call_eager"],
+                "us_per_call_with_kv_cache": m["us_per_call_with_kv_cache"], "gbs": m["gbs"]}
+    sampled("c1", c1)
+    sampled("c2", lambda: measure_fwd_bwd(ctx, peaks, flush, "c2", 300, 3))
+    sampled("c3", lambda: measure_fwd_bwd(ctx, peaks, flush, "c3", 50, 3))
+    sampled("c5", c5)
+    return out
+
+
 def run_small(args):
-    """Secondary, single-GPU reports for the small configurations (not the headline line):
-    c1 = fp32 forward B16 H4 S256 D64; c5 = the greedy no-KV-cache pattern, fp32 forward at every prefix
-    length 20..119 (100 calls), eager and replayed from one CUDA graph.  Device-resident inputs, CUDA events."""
+    """Single-GPU reports that are not the headline line: c1, c5 (see measure_c1, measure_c5), decode, linear, layer.
+    Device-resident inputs, CUDA events."""
     import torch
     from irontensor_b200 import _lib, context, raw
     torch.cuda.set_device(0)
@@ -391,41 +631,16 @@ def run_small(args):
     peaks = measured_peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(0x1A7E5EED + (1 if args.workload == "c1" else 5))
+    gen.manual_seed(0x1A7E5EED + 9)
 
     def timed(fn, reps, flush_l2):
-        ts = []
-        for i in range(reps):
-            if flush_l2:
-                flush.fill_(i & 0xFF)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) * 1e3)
-        return statistics.median(ts), min(ts)
+        return _timed_us(fn, reps, flush if flush_l2 else None)
 
     if args.workload == "c1":
-        B, H, S, D = 16, 4, 256, 64
-        q, k, v = (torch.randn((B, H, S, D), generator=gen, device="cuda") for _ in range(3))
-        o = torch.empty_like(q)
-        lse = torch.empty((B, H, S), device="cuda")
-
-        def f():
-            raw.fwd(_lib.IT_F32, B, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
-        for _ in range(max(args.warmup, 3)):
-            f()
-        med_cold, min_cold = timed(f, args.steps, True)
-        med_warm, min_warm = timed(f, args.steps, False)
-        flops, nbytes = 2.0 * B * H * S * S * D, 4 * B * H * S * D * 4 + B * H * S * 4
-        line = {"metric": "causal attention forward latency", "unit": "us", "value": med_cold, "higher_is_better": False,
-                "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "causal fp32 attention forward B16 H4 S256 D64", "l2": "flushed between calls (value); warm figures alongside"},
-                "us_min": min_cold, "us_warm_l2": med_warm, "gbs": nbytes / med_cold / 1e3, "gbs_warm_l2": nbytes / med_warm / 1e3,
-                "tflops": flops / med_cold / 1e6, "roofline": {"bound": "hbm", "achieved": nbytes / med_cold / 1e3, "peak": peaks["hbm"],
-                                                               "unit": "GB/s", "frac": nbytes / med_cold / 1e3 / peaks["hbm"], "traffic": None}}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(measure_c1(ctx, peaks, flush, args.steps, args.warmup)), flush=True)
+        return
+    if args.workload == "c5":
+        print(json.dumps(measure_c5(ctx, peaks, args.steps, args.warmup)), flush=True)
         return
     if args.workload == "decode":
         # One new token per sequence against a bf16 key/value cache (grouped heads): the op reads the cache once.
@@ -525,64 +740,6 @@ def run_small(args):
                              "frac": flops / med / 1e6 / peaks["bf16"], "traffic": None}}
         print(json.dumps(line), flush=True)
         return
-    # c5
-    H, D = 4, 64
-    lens = list(range(20, 120))
-    bufs = []
-    for S in lens:
-        q, k, v = (torch.randn((1, H, S, D), generator=gen, device="cuda") for _ in range(3))
-        bufs.append((S, q, k, v, torch.empty_like(q), torch.empty((1, H, S), device="cuda")))
-
-    def seq():
-        for S, q, k, v, o, lse in bufs:
-            raw.fwd(_lib.IT_F32, 1, H, S, D, True, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ctx=ctx)
-    for _ in range(max(args.warmup, 3)):
-        seq()
-    torch.cuda.synchronize()
-    med_eager, min_eager = timed(seq, args.steps, False)
-    side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        seq()
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph, stream=side):
-            seq()
-    torch.cuda.synchronize()
-    med_graph, min_graph = timed(graph.replay, args.steps, False)
-    # The same generation served from a key/value cache (it_attention_decode): each step attends one new token
-    # against the cached positions instead of recomputing the whole prefix.
-    kc = torch.randn((1, 128, H, D), generator=gen, device="cuda")
-    vc = torch.randn((1, 128, H, D), generator=gen, device="cuda")
-    qd = torch.randn((1, H, D), generator=gen, device="cuda")
-    od = torch.empty_like(qd)
-    nws = raw.decode_workspace_bytes(1, H, D)
-    wsd = torch.empty(nws, dtype=torch.uint8, device="cuda")
-
-    def seq_cached():
-        for S in lens:
-            raw.decode(_lib.IT_F32, 1, H, H, D, S, 128, qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), od.data_ptr(), None,
-                       wsd.data_ptr(), nws, ctx=ctx)
-    graph2 = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        seq_cached()
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph2, stream=side):
-            seq_cached()
-    torch.cuda.synchronize()
-    med_cached, _ = timed(graph2.replay, args.steps, False)
-    flops = sum(512.0 * S * S for S in lens)
-    nbytes = sum(4112.0 * S for S in lens)
-    line = {"metric": "greedy no-KV-cache attention forward, per-call latency", "unit": "us", "value": med_graph / len(lens),
-            "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "f32",
-            "data": "synthetic", "config": {"workload": "fp32 causal forward B1 H4 D64 at prefix lengths 20..119 (100 calls)",
-                                            "note": "value = one CUDA-graph replay of the 100 calls / 100; tensors stay in L2 (28.6 MB in total)"},
-            "us_per_call_eager": med_eager / len(lens), "us_per_call_graph_min": min_graph / len(lens),
-            "us_per_call_with_kv_cache": med_cached / len(lens),
-            "gbs": nbytes / med_graph / 1e3, "tflops": flops / med_graph / 1e6,
-            "roofline": {"bound": "hbm", "achieved": nbytes / med_graph / 1e3, "peak": peaks["hbm"], "unit": "GB/s",
-                         "frac": nbytes / med_graph / 1e3 / peaks["hbm"], "traffic": None,
-                         "note": "launch-latency bound: the HBM time of the longest call is 0.08 us"}}
-    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -595,6 +752,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end leg (profiling runs)")
     ap.add_argument("--no-bind", action="store_true", help="leave the process's CPU affinity alone")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the short reports on the other four configurations")
     ap.add_argument("--e2e-chunks", type=int, default=16,
                     help="groups the end-to-end leg cuts a rank's slices into (upload, kernels and download of "
                          "different groups overlap)")

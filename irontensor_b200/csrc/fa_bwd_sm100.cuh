@@ -18,7 +18,7 @@
 //                              reduce-add into an fp32 workspace (whole-line reductions in L2;
 //                              per-thread 16-byte atomics cost a third of the kernel's time).
 //   3. fa_bwd_finish_kernel  : dQ = bf16(workspace * 1/sqrt(D)).
-// Warp roles in (2): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocation,
+// Warp roles in (2): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocation, warp 3 dQ reduce issuer,
 // warps 4-7 and 8-11 two math groups (P^T, dS^T; a thread owns one key row and one half of the 128
 // query columns), warps 12-15 dQ drain.  Per query tile the tensor core sees, in order:
 //   dP^T(n) | [P^T(n) ready] dV(n), S^T(n+1) | [dS^T(n) ready] dQ(n), dK(n) | [dQ(n) drained] dP^T(n+1) ...
@@ -444,6 +444,37 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         if (ok) umma_commit(dkv_done);
       }
+    } else if (warp == 3) {
+      // ------------------------------------------------------------ dQ reduce issuer (one thread)
+      // Adds each staged 128 x 32 chunk of a dQ tile into the fp32 accumulator (TMA reduce-add) and hands the
+      // staging buffers back to the drain warps.  A thread of its own: the drain warps then never wait for a
+      // reduce to be issued or for its read of shared memory to finish.
+      if (lane == 0) {
+        bool ok = true;
+        int g = 0;
+        int qi = i0 - 1, bh_q = bh0;
+        for (int n = 0; n < n_iter && ok; ++n) {
+          if (++qi == n_q_tiles) {
+            qi = i0;
+            ++bh_q;
+          }
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c, ++g) {
+            const int buf = g & 1;
+            if (!mbar_wait(&dqs_full[buf], static_cast<uint32_t>(g >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX)) {
+              ok = false;
+              break;
+            }
+            tma_reduce_add_3d(&tmap_dq, smem + T::SMEM_DQS + buf * T::BLOCK_BYTES, c * 32, qi * T::BN, bh_q);
+            bulk_commit_group();
+            if (g >= 1) {   // the previous chunk's reduce has read the other buffer: hand it back
+              bulk_wait_group_read<1>();
+              mbar_arrive(&dqs_free[buf ^ 1]);
+            }
+          }
+        }
+        bulk_wait_group_all();   // shared memory must outlive the reads; results complete before exit
+      }
     }
   } else if (warp < 12) {
     if (run) {
@@ -601,17 +632,11 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int lane_base = (warp & 3) * 32;
       const int row = lane_base + lane;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + T::COL_DQ;
-      const bool issuer = (threadIdx.x == 12 * 32);
       const int swz = row & 7;
       bool ok = true;
       uint32_t r[D / 32][32];
       int g = 0;   // chunks handled so far
-      int qi = i0 - 1, bh_q = bh0;   // query tile and query slice of the tile being drained
       for (int n = 0; n < n_iter && ok; ++n) {
-        if (++qi == n_q_tiles) {
-          qi = i0;
-          ++bh_q;
-        }
         ok = mbar_wait_parked(dq_full, n & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -636,20 +661,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             *reinterpret_cast<uint4*>(dst + ((ch ^ swz) << 4)) =
                 make_uint4(r[c][ch * 4 + 0], r[c][ch * 4 + 1], r[c][ch * 4 + 2], r[c][ch * 4 + 3]);
           fence_proxy_async_smem();
-          mbar_arrive(&dqs_full[buf]);
-          if (issuer) {
-            if (mbar_wait_parked(&dqs_full[buf], use & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX)) {
-              tma_reduce_add_3d(&tmap_dq, stage, c * 32, qi * T::BN, bh_q);
-              bulk_commit_group();
-              if (g >= 1) {   // the previous chunk's reduce has read the other buffer: hand it back
-                bulk_wait_group_read<1>();
-                mbar_arrive(&dqs_free[buf ^ 1]);
-              }
-            }
-          }
+          mbar_arrive(&dqs_full[buf]);   // the reduce issuer (warp 3) takes it from here
         }
       }
-      if (issuer) bulk_wait_group_all();   // shared memory must outlive the reads; results complete before exit
     }
   }
 

@@ -686,9 +686,12 @@ class HostAttentionStep:
         self.dev = [[Tensor.empty([1, per, S, D], precision) for _ in range(4)] for _ in self.streams]
         self.done = [torch.cuda.Event() for _ in self.streams]
 
-    def run(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv):
+    def run(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv, copies_only=False):
         """All arguments: pinned torch tensors [n_slices, S, D].  Enqueues the whole step; the calling
-        stream continues only after every group's download has finished."""
+        stream continues only after every group's download has finished.  Nothing is waited for here: drain the
+        stream and check the device status (CommandBatch.sync(), context().poll_status()) before reading the
+        host tensors.  copies_only=True enqueues the same uploads and downloads on the same streams without the
+        kernels (what the host link alone costs; the downloaded bytes are then whatever the buffers held)."""
         torch = _torch()
         cur = torch.cuda.current_stream()
         start = torch.cuda.Event()
@@ -702,8 +705,11 @@ class HostAttentionStep:
                 st.wait_event(start)
                 tq, tk, tv, tdo = (Tensor(t._data[: n * self.S * self.D], shape, self.precision) for t in bufs)
                 tq.upload_from(hq[b0:b1]), tk.upload_from(hk[b0:b1]), tv.upload_from(hv[b0:b1]), tdo.upload_from(hdo[b0:b1])
-                out = flash_attention(tq, tk, tv, self.causal)
-                gq, gk, gv = attention_backward_recompute(tdo, tq, tk, tv, o=out, lse=out.lse, causal=self.causal)
+                if copies_only:
+                    out, gq, gk, gv = tq, tk, tv, tdo
+                else:
+                    out = flash_attention(tq, tk, tv, self.causal)
+                    gq, gk, gv = attention_backward_recompute(tdo, tq, tk, tv, o=out, lse=out.lse, causal=self.causal)
                 out.download_to(ho[b0:b1]), gq.download_to(hdq[b0:b1]), gk.download_to(hdk[b0:b1]), gv.download_to(hdv[b0:b1])
                 self.done[i % len(self.streams)].record(st)
         for ev in self.done:
