@@ -704,42 +704,151 @@ def run_small(args):
                              "frac": flops / med / 1e6 / peaks["bf16"], "traffic": None}}
         print(json.dumps(line), flush=True)
         return
-    if args.workload == "layer":
-        # The whole attention layer of the C4 shape on the packed q|k|v layout: fused projection with rotary epilogue,
-        # attention, output projection; then the three backward steps.  No layout op anywhere.
-        from irontensor_b200 import Tensor, Precision, attention_packed, attention_packed_backward, linear_backward, linear_forward, \
-            qkv_rope_forward
-        B, S, hidden, H, Hkv, D = 4, 8192, 2048, 16, 16, 128
-        n, W = B * S, (H + 2 * Hkv) * D
-        mk = lambda shape, sc: Tensor((torch.randn(shape, generator=gen, device="cuda") * sc).to(torch.bfloat16).reshape(-1), list(shape),
-                                      Precision.BF16)
-        x, wqkv, wo, dout = mk((B, S, hidden), 1.0), mk((W, hidden), 0.02), mk((hidden, H * D), 0.02), mk((n, hidden), 1.0)
 
-        def f():
-            qkv = qkv_rope_forward(x, wqkv, H, Hkv, D, 10000.0, 0, packed=True)
-            attn = attention_packed(qkv, H, Hkv, D, True)
-            out = linear_forward(attn.view([n, H * D]), wo)
-            d_attn, d_wo = linear_backward(dout, attn.view([n, H * D]), wo)
-            d_qkv = attention_packed_backward(d_attn.view([B, S, H, D]), qkv, attn, H, Hkv, D, True, rope_base=10000.0)
-            d_x, d_wqkv = linear_backward(d_qkv.view([n, W]), x.view([n, hidden]), wqkv)
-            return out, d_wo, d_x, d_wqkv
-        for _ in range(max(args.warmup, 3)):
-            f()
+
+def run_layer(args, rank, world, local_rank):
+    """The whole attention layer of the C4 shape, forward + backward, with the HEADS split over the ranks: every rank
+    projects with its rows of [Wq; Wk; Wv] (one GEMM with the rotary epilogue, packed q|k|v layout), attends over its
+    heads, multiplies by its columns of Wo -- and the partial outputs are summed by an NCCL all-reduce, the one real
+    exchange step around the path (src/train/forward.rs:146 of the reference; backward: the gradient of the layer's
+    input, src/train/backward.rs:139-147, is the second sum over ranks).  Rank 0 also runs the unsharded layer and
+    compares.  No library GEMM is given a peer's memory; the all-reduce is NCCL's own."""
+    import torch
+    import torch.distributed as dist
+    from irontensor_b200 import (Precision, Tensor, attention_packed, attention_packed_backward, context, linear_backward,
+                                 linear_forward, qkv_rope_forward, raw)
+    from irontensor_b200.sharding import head_shard, out_projection_all_reduce, qkv_weight_rows
+    torch.cuda.set_device(local_rank)
+    ctx = context(local_rank)
+    peaks = measured_peaks()
+    B, S, hidden, H, Hkv, D = 4, 8192, 2048, 16, 16, 128
+    n = B * S
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x1A7E5EED + 6)      # the same seed on every rank: every rank generates the same full tensors
+    rnd = lambda shape, sc: (torch.randn(shape, generator=gen, device="cuda") * sc).to(torch.bfloat16)
+    x, wq, wk, wv = rnd((B, S, hidden), 1.0), rnd((H * D, hidden), 0.02), rnd((Hkv * D, hidden), 0.02), rnd((Hkv * D, hidden), 0.02)
+    wo, dout = rnd((hidden, H * D), 0.02), rnd((n, hidden), 1.0)
+    T = lambda t: Tensor(t.contiguous().reshape(-1), list(t.shape), Precision.BF16)
+
+    def make(world_, rank_):
+        qb, qe, kb, ke = head_shard(H, Hkv, world_, rank_)
+        (q0, q1), (k0, k1), (v0, v1) = qkv_weight_rows(H, Hkv, D, world_, rank_)
+        hl, hkvl = qe - qb, ke - kb
+        w_l, wo_l = T(torch.cat([wq[q0:q1], wk[k0:k1], wv[v0:v1]], 0)), T(wo[:, q0:q1])
+        tx, tdout = T(x), T(dout)
+        width = (hl + 2 * hkvl) * D
+
+        chunks = max(args.layer_chunks, 1) if world_ > 1 else 1
+        rows = n // chunks
+
+        def step(reduce):
+            """reduce: False = no exchange; True = one blocking all-reduce per sum; "overlap" = the two GEMMs whose results
+            are summed over ranks run in row chunks, each chunk's all-reduce (NCCL's stream) under the next chunk's GEMM."""
+            qkv = qkv_rope_forward(tx, w_l, hl, hkvl, D, 10000.0, 0, packed=True)
+            attn = attention_packed(qkv, hl, hkvl, D, True)
+            pending = []
+            if reduce == "overlap":
+                out = Tensor.empty([n, hidden], Precision.BF16)
+                a2 = attn.torch().view(n, hl * D)
+                for c in range(chunks):
+                    r0 = c * rows
+                    raw.linear_fwd(rows, hl * D, hidden, a2[r0:r0 + rows].data_ptr(), wo_l.data_ptr(), out.torch()[r0:r0 + rows].data_ptr())
+                    pending.append(dist.all_reduce(out.torch()[r0:r0 + rows], async_op=True))
+            else:
+                out = linear_forward(attn.view([n, hl * D]), wo_l)                   # this rank's partial [n, hidden]
+                if reduce:
+                    out_projection_all_reduce(out.torch())
+            d_attn, d_wo = linear_backward(tdout, attn.view([n, hl * D]), wo_l)
+            d_qkv = attention_packed_backward(d_attn.view([B, S, hl, D]), qkv, attn, hl, hkvl, D, True, rope_base=10000.0)
+            if reduce == "overlap":
+                d_x, d_w = Tensor.empty([n, hidden], Precision.BF16), Tensor.empty([width, hidden], Precision.FP32)
+                g2, x2 = d_qkv.torch().view(n, width), tx.torch().view(n, hidden)
+                for c in range(chunks):
+                    r0 = c * rows
+                    raw.linear_bwd(rows, hidden, width, g2[r0:r0 + rows].data_ptr(), x2[r0:r0 + rows].data_ptr(), w_l.data_ptr(),
+                                   d_x.torch()[r0:r0 + rows].data_ptr(), None)
+                    pending.append(dist.all_reduce(d_x.torch()[r0:r0 + rows], async_op=True))
+                raw.linear_bwd(n, hidden, width, g2.data_ptr(), x2.data_ptr(), w_l.data_ptr(), None, d_w.data_ptr())   # no exchange
+                for wk_ in pending:
+                    wk_.wait()
+            else:
+                d_x, d_w = linear_backward(d_qkv.view([n, width]), tx.view([n, hidden]), w_l)
+                if reduce:
+                    out_projection_all_reduce(d_x.torch())
+            return out, d_x, d_wo, d_w
+        return step, hl, hkvl
+
+    step, hl, hkvl = make(world, rank)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
         l0 = ctx.launch_count()
-        med, mn = timed(f, args.steps, True)
-        launches = ctx.launch_count() - l0
-        gemm = 2.0 * n * hidden * (W + H * D)
-        flops = 3 * gemm + 7.0 * B * H * S * S * D
-        line = {"metric": "attention layer fwd+bwd TFLOP/s (projections + rotary + causal attention)", "unit": "TFLOP/s",
-                "value": flops / med / 1e6, "higher_is_better": True, "n_gpus": 1, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "dtype": "bf16", "data": "synthetic", "ms_per_step": med / 1e3,
-                "config": {"workload": "attention layer B4 S8192 hidden 2048, 16 heads of 128, packed q|k|v, bf16",
-                           "flops": {"projections": 3 * gemm, "attention": 7.0 * B * H * S * S * D}},
-                "gpu_launches": launches,
-                "roofline": {"bound": "tensor", "achieved": flops / med / 1e6, "peak": peaks["bf16"], "unit": "TFLOP/s",
-                             "frac": flops / med / 1e6 / peaks["bf16"], "traffic": None}}
-        print(json.dumps(line), flush=True)
+        barrier()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for a, b in ev:
+            flush.fill_(1)
+            a.record()
+            fn()
+            b.record()
+        barrier()
+        ctx.poll_status()
+        return max_over_ranks(sum(a.elapsed_time(b) for a, b in ev) / steps), ctx.launch_count() - l0
+
+    ms, launches = timed(lambda: step(True))
+    ms_local, _ = timed(lambda: step(False))              # the same without the two all-reduces
+    ms_overlap = timed(lambda: step("overlap"))[0] if (world > 1 and args.layer_chunks > 0) else None
+    buf = torch.empty((n, hidden), dtype=torch.bfloat16, device="cuda")
+    ms_ar, _ = timed(lambda: out_projection_all_reduce(buf)) if world > 1 else (0.0, 0)
+    # the summed results against the unsharded layer on rank 0 (same seed, same kernels, all heads on one GPU)
+    out, d_x, _, _ = step(True)
+    check = None
+    if rank == 0:
+        full_step, _, _ = make(1, 0)
+        f_out, f_dx, _, _ = full_step(False)
+        torch.cuda.synchronize()
+        rel = lambda a, b: float((a.torch().float() - b.torch().float()).norm() / b.torch().float().norm())
+        check = {"against": "the unsharded layer on rank 0, same seed", "out_rel_l2": rel(out, f_out), "dx_rel_l2": rel(d_x, f_dx),
+                 "out_max_abs": float((out.torch().float() - f_out.torch().float()).abs().max()),
+                 "note": "each rank's partial is rounded to bf16 before the sum"}
+        assert check["out_rel_l2"] < 1e-2 and check["dx_rel_l2"] < 1e-2, check
+    barrier()
+    if rank != 0:
         return
+    gemm = 2.0 * n * hidden * ((H + 2 * Hkv) * D + H * D)
+    flops = 3 * gemm + 7.0 * B * H * S * S * D
+    ar_bytes = n * hidden * 2
+    line = {"metric": "attention layer fwd+bwd TFLOP/s (projections + rotary + causal attention), heads split over the GPUs",
+            "unit": "TFLOP/s", "value": flops / ms / 1e9, "higher_is_better": True, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "dtype": "bf16", "data": "synthetic", "ms_per_step": ms, "scaling": "strong",
+            "config": {"workload": "attention layer B4 S8192 hidden 2048, 16 heads of 128, packed q|k|v, bf16",
+                       "sharding": f"{hl} of {H} heads per rank; output projection and input gradient summed by NCCL all-reduce",
+                       "flops": {"projections": 3 * gemm, "attention": 7.0 * B * H * S * S * D}},
+            "all_reduce": {"per_step": 2 if world > 1 else 0, "bytes_each": ar_bytes, "ms_each_alone": ms_ar,
+                           "bus_gbs_alone": (2 * (world - 1) / world * ar_bytes / (ms_ar * 1e-3) / 1e9) if world > 1 else None,
+                           "ms_per_step_without": ms_local, "share_of_step": (ms - ms_local) / ms if world > 1 else 0.0,
+                           "ms_per_step_chunked_overlap": ms_overlap,
+                           "chunked_overlap": (f"{args.layer_chunks} row chunks per summed GEMM, each chunk's all-reduce issued under the "
+                                               "next chunk's GEMM; slower than one blocking all-reduce: NCCL's kernel cannot run "
+                                               "beside a GEMM that holds every SM") if ms_overlap is not None else None},
+            "check": check, "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9 / world, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                         "frac": flops / ms / 1e9 / world / peaks["bf16"], "traffic": None, "note": "per GPU"}}
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -756,6 +865,9 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=16,
                     help="groups the end-to-end leg cuts a rank's slices into (upload, kernels and download of "
                          "different groups overlap)")
+    ap.add_argument("--layer-chunks", type=int, default=0,
+                    help="--workload layer on several GPUs: also time the variant that runs the two summed GEMMs in this many "
+                         "row chunks with each chunk's all-reduce under the next chunk's GEMM (0: skip)")
     ap.add_argument("--slices", type=int, default=0,
                     help="use only this many (batch x head) slices of the workload (small profiling cases)")
     args = ap.parse_args()
@@ -770,9 +882,22 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", port, os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
-    if args.workload in ("c1", "c5", "decode", "linear", "layer"):
+    if args.workload in ("c1", "c5", "decode", "linear"):
         if rank == 0:
             run_small(args)
+        return
+    if args.workload == "layer":
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        try:
+            run_layer(args, rank, world, local_rank)
+        finally:
+            if world > 1:
+                import torch.distributed as dist
+                dist.destroy_process_group()
         return
     if args.impl == "reference":
         run_reference(args, rank, world)
