@@ -319,7 +319,7 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     sampler.mark()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    fwd_ms, bwd_ms = [], []
+    fwd_ms, bwd_ms, prep_ms, fin_ms = [], [], [], []
     for i in range(steps):
         flush.fill_(i & 0xFF)                 # evict the previous step's tensors from L2 (outside the event pair)
         ev[i][0].record()
@@ -328,6 +328,8 @@ def run_ours(args, rank, world, local_rank):
         if nbh:
             fwd_ms.append(ctx.kernel_ms(0))   # waits for this step's kernels
             bwd_ms.append(ctx.kernel_ms(1))
+            prep_ms.append(ctx.kernel_ms(2))
+            fin_ms.append(ctx.kernel_ms(3))
     barrier()
     launches = ctx.launch_count() - launches0
     ctx.poll_status()
@@ -405,6 +407,9 @@ def run_ours(args, rank, world, local_rank):
         "frac": ach / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload if world == 1 else None),
         "peak_source": peaks["source"] + " (burst)", "avg_launch_ms": bwd_avg_ms,
         "frac_of_sustained_peak": ach / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
+        "profiler_tag": ctx.kernel_tag(1),
+        "other_kernels_ms": {ctx.kernel_tag(2): statistics.mean(prep_ms) if prep_ms else None,
+                             ctx.kernel_tag(3): statistics.mean(fin_ms) if fin_ms else None},
         "forward_kernel": {"kernel": "fa_fwd_pp_sm100_kernel" if (D == 128 and S >= 4096) else "fa_fwd_sm100_kernel",
                            "avg_launch_ms": fwd_avg_ms,
                            "achieved": flops_fwd(nbh, S, D) / (fwd_avg_ms * 1e-3) / 1e12,

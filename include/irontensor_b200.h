@@ -119,7 +119,7 @@ it_status it_flash_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype,
  * descriptors, so those copies disappear.  Same math, dispatch, workspace size
  * (it_flash_attention_bwd_workspace_bytes with the same B, H, S, D) and error codes as the [B,H,S,D] entry
  * points; lse stays [batch, heads, seq].  K/V with another sequence length than Q (which the reference
- * allows when not causal) are not taken. */
+ * allows when not causal): it_attention_cross_fwd below. */
 it_status it_attention_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq, int32_t heads,
                            int32_t head_dim, int32_t causal, const void* q, const void* k, const void* v, void* o,
                            float* lse);
@@ -127,6 +127,16 @@ it_status it_attention_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32
                            int32_t head_dim, int32_t causal, const void* q, const void* k, const void* v, const void* o,
                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* workspace,
                            size_t workspace_bytes);
+
+/* attention(q, k, v, causal = false) with a key/value length different from the query length: the reference reads
+ * kv_seq_len from K (src/ops/attention.rs:304) and only its causal branch requires it to equal q_seq_len (:349-352).
+ * q, o: [batch, seq_q, heads, head_dim]; k, v: [batch, seq_kv, heads, head_dim]; lse [batch, heads, seq_q] (may be
+ * null).  Never causal.  seq_q == seq_kv is it_attention_fwd with causal = 0 (tensor-core kernels for bf16);
+ * otherwise the CUDA-core kernels run (fp32 as in the reference, or bf16), since a query and a key length that
+ * differ occur in the reference only outside its training path.  The reference has no backward for this op. */
+it_status it_attention_cross_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t batch, int32_t seq_q,
+                                 int32_t seq_kv, int32_t heads, int32_t head_dim, const void* q, const void* k,
+                                 const void* v, void* o, float* lse);
 
 /* Grouped-query attention on [batch, seq, heads, head_dim] queries and [batch, seq, kv_heads, head_dim]
  * keys/values, kv_heads dividing heads; query head h reads K/V head h / (heads / kv_heads).  The reference
@@ -277,9 +287,13 @@ it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out);
  * which measures host encode time.  While enabled, each it_flash_attention_fwd / _bwd call
  * records a CUDA event before and after its main kernel on the call's stream.
  * it_ctx_kernel_ms waits for the most recent such pair and returns the time between them
- * (which = 0: forward kernel, 1: backward main kernel). */
+ * (which = 0: forward kernel, 1: backward main kernel, 2: backward prepare pass, 3: backward finish pass; 2 and 3
+ * exist for the tensor-core backward only).  it_ctx_kernel_tag gives the reference's profiler tag for what a timer
+ * covers: its composed backward reports attn_bwd/recompute, /grad_v, /grad_p and /grad_qk (src/train/helpers.rs:
+ * 126-183), all of which are inside the one main kernel here. */
 it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable);
 it_status it_ctx_kernel_ms(it_ctx* ctx, int32_t which, float* ms);
+const char* it_ctx_kernel_tag(int32_t which);
 
 /* ---- self tests (no reference counterpart; they pin the hardware descriptors the kernels use) */
 

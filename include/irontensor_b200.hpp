@@ -280,8 +280,8 @@ inline std::tuple<Tensor, Tensor, Tensor> attention_backward_recompute(const Ten
 }
 
 // src/ops/attention.rs:286-377: [batch, seq, heads, head_dim] in and out.  The kernels read and write
-// this layout in place, so the transposes the reference runs around its GEMMs are gone; K/V with
-// another sequence length than Q (allowed there when not causal) is not taken.  The result carries
+// this layout in place, so the transposes the reference runs around its GEMMs are gone.  K/V may have
+// another sequence length than Q when not causal (src/ops/attention.rs:304,349-352).  The result carries
 // `.lse` ([batch, heads, seq]) for attention_backward.
 inline Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, bool causal) {
   require(q.shape().size() == 4, "Q must be 4D [batch, seq, heads, dim]");
@@ -296,7 +296,14 @@ inline Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, bool 
   Tensor out = Tensor::zeros({B, S, H, D}, q.precision());
   out.lse = std::make_shared<Tensor>(Tensor::zeros({B, H, S}, Precision::FP32));
   if (B == 0 || S == 0 || k.shape()[1] == 0) return out;
-  require(k.shape()[1] == S, "attention(): only K/V of the same sequence length as Q are fused");
+  if (causal) require(k.shape()[1] == S, "Causal attention requires Q and K to have same seq_len");
+  if (k.shape()[1] != S) {
+    check(it_attention_cross_fwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
+                                 static_cast<int32_t>(B), static_cast<int32_t>(S), static_cast<int32_t>(k.shape()[1]),
+                                 static_cast<int32_t>(H), static_cast<int32_t>(D), q.ptr(), k.ptr(), v.ptr(), out.ptr(),
+                                 static_cast<float*>(out.lse->ptr())));
+    return out;
+  }
   check(it_attention_fwd(Context::global().raw(), Context::global().stream(), dtype_code(q.precision()),
                          static_cast<int32_t>(B), static_cast<int32_t>(S), static_cast<int32_t>(H), static_cast<int32_t>(D),
                          causal ? 1 : 0, q.ptr(), k.ptr(), v.ptr(), out.ptr(), static_cast<float*>(out.lse->ptr())));

@@ -21,7 +21,7 @@ _c = ctypes
 _vp = _c.c_void_p
 _i32 = _c.c_int32
 
-# name -> argtypes; every function returns it_status (int32) except it_last_error.
+# name -> argtypes; every function returns it_status (int32) except it_last_error and it_ctx_kernel_tag.
 SIGNATURES = {
     "it_ctx_create": [_c.c_int, _c.POINTER(_vp)],
     "it_ctx_destroy": [_vp],
@@ -47,6 +47,7 @@ SIGNATURES = {
     "it_flash_attention_bwd_workspace_bytes": [_c.c_int, _i32, _i32, _i32, _i32, _c.POINTER(_c.c_size_t)],
     "it_flash_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
     "it_attention_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
+    "it_attention_cross_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "it_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
     "it_attention_gqa_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "it_attention_gqa_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
@@ -95,6 +96,8 @@ def load():
             fn.restype = _i32
         lib.it_last_error.argtypes = []
         lib.it_last_error.restype = _c.c_char_p
+        lib.it_ctx_kernel_tag.argtypes = [_i32]
+        lib.it_ctx_kernel_tag.restype = _c.c_char_p
         _lib = lib
     return _lib
 

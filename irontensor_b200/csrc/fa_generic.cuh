@@ -46,8 +46,9 @@ template <> __device__ __forceinline__ void st_from_f32<__nv_bfloat16>(__nv_bflo
 template <typename ST, int DP>
 __global__ void __launch_bounds__(256)
 fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const ST* __restrict__ v,
-                      ST* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
+                      ST* __restrict__ o, float* __restrict__ lse, int S, int Skv, int D, int causal, float scale_log2,
                       TensorStrides st, TensorStrides skv) {
+  // S query rows against Skv keys; a causal launch has Skv == S (src/ops/attention.rs:349-352).
   constexpr int BM = 64;
   constexpr int BN = (DP >= 128) ? 32 : 64;
   constexpr int NCH = DP / 16;              // float4 chunks per thread
@@ -81,7 +82,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
   float m_run = -INFINITY, l_run = 0.f;
 
   const int row_hi = min(S, (rt + 1) * BM) - 1;               // last valid row of this CTA
-  const int k_end = causal ? (row_hi + 1) : S;                // keys [0, k_end)
+  const int k_end = causal ? (row_hi + 1) : Skv;              // keys [0, k_end)
   for (int k0 = 0; k0 < k_end; k0 += BN) {
     const int nk = min(BN, k_end - k0);
     __syncthreads();
@@ -169,7 +170,7 @@ fa_fwd_generic_kernel(const ST* __restrict__ q, const ST* __restrict__ k, const 
 template <int NJ, int RW, int RB = 16>
 __global__ void __launch_bounds__(32 * (RB / RW))
 fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                       float* __restrict__ o, float* __restrict__ lse, int S, int D, int causal, float scale_log2,
+                       float* __restrict__ o, float* __restrict__ lse, int S, int Skv, int D, int causal, float scale_log2,
                        TensorStrides st, TensorStrides skv) {
   constexpr int TK = 32, NT = 32 * (RB / RW);   // RB rows per CTA: RB / RW warps, RW rows each
   extern __shared__ __align__(16) float sm[];
@@ -188,7 +189,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
   const size_t RS = static_cast<size_t>(st.row);
   const size_t kbase = static_cast<size_t>(skv.slice(bh));   // the K/V head this query head reads
   const size_t KRS = static_cast<size_t>(skv.row);
-  const int k_end_cta = causal ? min(S, r0 + RB) : S;
+  const int k_end_cta = causal ? min(S, r0 + RB) : Skv;
   const int n_tiles = (k_end_cta + TK - 1) / TK;
 
   auto load_tile = [&](int tile, int buf) {
@@ -227,7 +228,7 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
     const int row = r0 + warp * RW + w;
     m_run[w] = -INFINITY;
     l_run[w] = 0.f;
-    lim[w] = (row < S) ? (causal ? row : S - 1) : -1;
+    lim[w] = (row < S) ? (causal ? row : Skv - 1) : -1;
     lim_max = max(lim_max, lim[w]);
 #pragma unroll
     for (int jj = 0; jj < NJ; ++jj) acc[w][jj] = 0.f;

@@ -60,8 +60,10 @@ struct it_ctx {
   std::mutex status_mutex;      // h_status and status_stream are shared by every thread using the context
   EncodeTiledFn encode = nullptr;
   bool timing = false;          // record events around the main kernels
-  cudaEvent_t ev[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};   // [fwd|bwd][start|stop]
-  bool ev_valid[2] = {false, false};
+  // [forward | backward main | backward prepare | backward finish][start | stop]; the prepare pass starts where the
+  // previous timer stopped only in time, not in events: three pairs share the boundaries prepare|main|finish
+  cudaEvent_t ev[4][2] = {};
+  bool ev_valid[4] = {false, false, false, false};
   std::atomic<uint64_t> launches{0};
 };
 struct it_stream {
@@ -158,7 +160,9 @@ int round_dp(int D) { return D <= 16 ? 16 : D <= 32 ? 32 : D <= 64 ? 64 : 128; }
 
 template <typename ST>
 it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, int causal, const void* q, const void* k,
-                        const void* v, void* o, float* lse, const it::TensorStrides& st, const it::TensorStrides& skv) {
+                        const void* v, void* o, float* lse, const it::TensorStrides& st, const it::TensorStrides& skv,
+                        int Skv = -1) {
+  if (Skv < 0) Skv = S;   // self-attention; a different key/value length only comes from it_attention_cross_fwd
   const float scale = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;   // exp2 domain
   const dim3 grid((S + 63) / 64, BH);
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
@@ -177,18 +181,18 @@ it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, 
     const int rw = (static_cast<long long>(g16.x) * g16.y <= ctx->sm_count) ? 2 : 4;
     const unsigned nt = 32u * (16u / static_cast<unsigned>(rw));
     if (D <= 32) {
-      if (rw == 2) it::fa_fwd_rows_f32_kernel<1, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
-      else it::fa_fwd_rows_f32_kernel<1, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
+      if (rw == 2) it::fa_fwd_rows_f32_kernel<1, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      else it::fa_fwd_rows_f32_kernel<1, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
     } else if (D <= 64 && static_cast<long long>(g16.x) * g16.y > 4LL * ctx->sm_count) {
       // Many CTAs per SM (the reference's TINY training shape, batch 16 x 4 heads x 256 keys): the kernel is
       // bound by its shared-memory loads, and 32-row CTAs with eight rows per warp use every K chunk and V
       // row for twice as many rows (49 against 53 us on that shape).
       const int smem32 = (32 * D + 4 * 32 * (D + 4) + 32 * 32) * 4;
       const dim3 g32((S + 31) / 32, BH);
-      it::fa_fwd_rows_f32_kernel<2, 8, 32><<<g32, 128, smem32, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
+      it::fa_fwd_rows_f32_kernel<2, 8, 32><<<g32, 128, smem32, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
     } else if (D <= 64) {
-      if (rw == 2) it::fa_fwd_rows_f32_kernel<2, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
-      else it::fa_fwd_rows_f32_kernel<2, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
+      if (rw == 2) it::fa_fwd_rows_f32_kernel<2, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      else it::fa_fwd_rows_f32_kernel<2, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
     } else {
       static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
       if (!attr_set[ctx->device & 15]) {
@@ -198,18 +202,18 @@ it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, 
                                      (16 * 128 + 4 * 32 * 132 + 512) * 4));
         attr_set[ctx->device & 15] = true;
       }
-      if (rw == 2) it::fa_fwd_rows_f32_kernel<4, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
-      else it::fa_fwd_rows_f32_kernel<4, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, D, causal, scale, st, skv);
+      if (rw == 2) it::fa_fwd_rows_f32_kernel<4, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      else it::fa_fwd_rows_f32_kernel<4, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
     }
     ctx->launches += 1;
     IT_CUDA(cudaGetLastError());
     return IT_OK;
   }
   switch (round_dp(D)) {
-    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
-    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
-    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
-    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, D, causal, scale, st, skv); break;
+    case 16: it::fa_fwd_generic_kernel<ST, 16><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, Skv, D, causal, scale, st, skv); break;
+    case 32: it::fa_fwd_generic_kernel<ST, 32><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, Skv, D, causal, scale, st, skv); break;
+    case 64: it::fa_fwd_generic_kernel<ST, 64><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, Skv, D, causal, scale, st, skv); break;
+    default: it::fa_fwd_generic_kernel<ST, 128><<<grid, 256, 0, s>>>(qq, kk, vv, oo, lse, S, Skv, D, causal, scale, st, skv); break;
   }
   ctx->launches += 1;
   IT_CUDA(cudaGetLastError());
@@ -340,6 +344,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   const size_t n_dq = static_cast<size_t>(BH) * S * D;
   const long long rows_pad = static_cast<long long>(BH) * w.S_pad;
+  if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[2][0], s));
   it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad / 8 + 7) / 8), 256, 0, s>>>(   // 8 rows per warp, 8 warps
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, dq_accum, S,
       w.S_pad, BH, stv);
@@ -359,15 +364,24 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const int n_kt = (S + 127) / 128;
-  if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
+  if (ctx->timing) {
+    IT_CUDA(cudaEventRecord(ctx->ev[2][1], s));
+    ctx->ev_valid[2] = true;
+    IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
+  }
   it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p, rf);
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
+    IT_CUDA(cudaEventRecord(ctx->ev[3][0], s));
   }
   const size_t n4 = n_dq / 4;
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
       dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, sq, rf);
+  if (ctx->timing) {
+    IT_CUDA(cudaEventRecord(ctx->ev[3][1], s));
+    ctx->ev_valid[3] = true;
+  }
   ctx->launches += 3;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -583,7 +597,7 @@ it_status it_ctx_destroy(it_ctx* ctx) {
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
   if (ctx->status_stream != nullptr) cudaStreamDestroy(ctx->status_stream);
-  for (int a = 0; a < 2; ++a)
+  for (int a = 0; a < 4; ++a)
     for (int b = 0; b < 2; ++b)
       if (ctx->ev[a][b] != nullptr) cudaEventDestroy(ctx->ev[a][b]);
   delete ctx;
@@ -789,6 +803,22 @@ it_status it_attention_gqa_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, i
                                int32_t Hkv, int32_t D, int32_t causal, const void* q, const void* k, const void* v,
                                void* o, float* lse) {
   return attention_fwd_impl(ctx, stream, dtype, B, H, Hkv, S, D, causal, q, k, v, o, lse, true);
+}
+
+it_status it_attention_cross_fwd(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B, int32_t Sq, int32_t Skv, int32_t H,
+                                 int32_t D, const void* q, const void* k, const void* v, void* o, float* lse) {
+  if (Sq == Skv) return attention_fwd_impl(ctx, stream, dtype, B, H, H, Sq, D, 0, q, k, v, o, lse, true);
+  it_status st = check_common(ctx, stream, dtype, B, H, Sq, D);
+  if (st != IT_OK) return st;
+  if (Skv < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  if (B == 0 || Sq == 0 || Skv == 0 || H == 0) return IT_OK;   // src/ops/attention.rs:313-315: the zeroed output is the caller's
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(IT_ERR_ALIGNMENT, "q, k, v and o must be 16-byte aligned");
+  IT_CUDA(cudaSetDevice(ctx->device));
+  const it::TensorStrides sq = strides_bshd(H, Sq, D), skv = strides_bshd(H, Skv, D);
+  return dtype == IT_F32 ? launch_fwd_generic<float>(ctx, stream->s, B * H, Sq, D, 0, q, k, v, o, lse, sq, skv, Skv)
+                         : launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, B * H, Sq, D, 0, q, k, v, o, lse, sq, skv, Skv);
 }
 
 it_status it_flash_attention_bwd_workspace_bytes(it_dtype dtype, int32_t B, int32_t H, int32_t S, int32_t D,
@@ -1138,7 +1168,7 @@ it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable) {
   if (ctx == nullptr) return fail(IT_ERR_INVALID_ARG, "null context");
   IT_CUDA(cudaSetDevice(ctx->device));
   if (enable && ctx->ev[0][0] == nullptr) {
-    for (int a = 0; a < 2; ++a)
+    for (int a = 0; a < 4; ++a)
       for (int b = 0; b < 2; ++b) IT_CUDA(cudaEventCreate(&ctx->ev[a][b]));
   }
   ctx->timing = enable != 0;
@@ -1147,11 +1177,23 @@ it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable) {
 
 it_status it_ctx_kernel_ms(it_ctx* ctx, int32_t which, float* ms) {
   if (ctx == nullptr || ms == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
-  if (which < 0 || which > 1) return fail(IT_ERR_INVALID_ARG, "which must be 0 (forward) or 1 (backward)");
+  if (which < 0 || which > 3)
+    return fail(IT_ERR_INVALID_ARG, "which must be 0 (forward), 1 (backward main), 2 (backward prepare) or 3 (backward finish)");
   if (!ctx->ev_valid[which]) return fail(IT_ERR_INVALID_ARG, "no timed launch of that kernel yet");
   IT_CUDA(cudaEventSynchronize(ctx->ev[which][1]));
   IT_CUDA(cudaEventElapsedTime(ms, ctx->ev[which][0], ctx->ev[which][1]));
   return IT_OK;
+}
+
+const char* it_ctx_kernel_tag(int32_t which) {
+  // The reference's profiler names (src/ops/flash_attention.rs:77; src/train/helpers.rs:126-183) for what each timer covers.
+  switch (which) {
+    case 0: return "FlashAttention";
+    case 1: return "attn_bwd/recompute+grad_v+grad_p+grad_qk";
+    case 2: return "attn_bwd/prepare";
+    case 3: return "attn_bwd/finish";
+    default: return "";
+  }
 }
 
 it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out) {

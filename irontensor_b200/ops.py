@@ -71,8 +71,12 @@ class _Context:
     def enable_kernel_timing(self, on=True):
         _lib.check(self.lib.it_ctx_enable_kernel_timing(self.handle, int(on)))
 
+    def kernel_tag(self, which):
+        """The reference's profiler tag for what timer `which` covers (FlashAttention, attn_bwd/...)."""
+        return self.lib.it_ctx_kernel_tag(which).decode()
+
     def kernel_ms(self, which):
-        """Device time of the most recent forward (0) or backward-main (1) kernel."""
+        """Device time of the most recent forward (0), backward-main (1), backward-prepare (2) or backward-finish (3) kernel."""
         ms = ctypes.c_float()
         _lib.check(self.lib.it_ctx_kernel_ms(self.handle, which, ctypes.byref(ms)))
         return ms.value
@@ -435,8 +439,8 @@ def attention(q, k, v, causal):
     Same math as flash_attention.  The kernels read and write this layout in place (strided TMA
     descriptors), so the transposes the reference runs around its attention are gone.  Accepts FP32
     like the reference, and BF16.  The result carries `.lse` ([batch, heads, seq]) for
-    attention_backward.  The reference lets K/V have another sequence length when not causal; that
-    case is not taken here."""
+    attention_backward.  K/V may have another sequence length when not causal, as in the reference
+    (src/ops/attention.rs:304,349-352); that case runs on the CUDA-core kernels."""
     p = q.precision()
     assert k.precision() is p and v.precision() is p
     qs, ks, vs = q.shape(), k.shape(), v.shape()
@@ -450,10 +454,15 @@ def attention(q, k, v, causal):
     assert vs[1] == ks[1], "K and V seq_len must match"
     if B == 0 or Sq == 0 or ks[1] == 0:
         return Tensor.zeros([B, Sq, H, D], p)
-    if ks[1] != Sq:
-        raise NotImplementedError("attention(): K/V sequence length differs from Q's; only self-attention is fused")
+    if causal:
+        assert ks[1] == Sq, "Causal attention requires Q and K to have same seq_len"      # src/ops/attention.rs:349-352
     out = Tensor.empty([B, Sq, H, D], p)
     out.lse = Tensor.empty([B, H, Sq], Precision.FP32)
+    if ks[1] != Sq:
+        c = context()
+        _lib.check(c.lib.it_attention_cross_fwd(c.handle, c.stream(), _dtype_code(p), B, Sq, ks[1], H, D, q.data_ptr(),
+                                                k.data_ptr(), v.data_ptr(), out.data_ptr(), out.lse.data_ptr()))
+        return out
     raw.fwd_bshd(_dtype_code(p), B, Sq, H, D, causal, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                  out.lse.data_ptr())
     return out

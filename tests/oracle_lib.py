@@ -87,6 +87,25 @@ def bwd(q, k, v, d_o, causal=True, bh_range=None):
     return dq, dk, dv
 
 
+def cross_fwd(q, k, v):
+    """Non-causal attention of q [B,H,Sq,D] over k, v [B,H,Skv,D] with Sq != Skv, which the reference's attention()
+    accepts (src/ops/attention.rs:304,349-352).  Without a mask every query row is independent of the other query
+    rows, so the oracle's equal-length forward is run on chunks of at most Skv query rows padded to Skv with zeros."""
+    q, k, v = _c(q), _c(k), _c(v)
+    B, H, Sq, D = q.shape
+    Skv = k.shape[2]
+    o = np.zeros_like(q)
+    lse = np.zeros((B, H, Sq), np.float32)
+    for r0 in range(0, Sq, Skv):
+        n = min(Skv, Sq - r0)
+        qp = np.zeros((B, H, Skv, D), np.float32)
+        qp[:, :, :n] = q[:, :, r0:r0 + n]
+        oc, lc = fwd(qp, k, v, causal=False)
+        o[:, :, r0:r0 + n] = oc[:, :, :n]
+        lse[:, :, r0:r0 + n] = lc[:, :, :n]
+    return o, lse
+
+
 def f32_to_bf16_bits(x):
     x = _c(x)
     out = np.zeros(x.shape, np.uint16)

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     assert len(declared) >= 25
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
-    assert set(_lib.SIGNATURES) | {"it_last_error"} == declared
+    assert set(_lib.SIGNATURES) | {"it_last_error", "it_ctx_kernel_tag"} == declared
 
 
 def test_argument_checks_that_need_no_gpu():

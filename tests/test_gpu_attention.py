@@ -497,6 +497,29 @@ def test_bshd_layout_matches_bhsd(it_ctx, shape, bf16):
     assert np.abs(back(o2) - ref).max() <= tol
 
 
+@pytest.mark.parametrize("B,Sq,Skv,H,D,bf16", [(2, 5, 37, 3, 16, False), (1, 200, 64, 2, 64, False), (2, 1, 77, 4, 32, False),
+                                               (1, 70, 300, 2, 128, True), (1, 128, 384, 2, 64, True), (1, 300, 40, 2, 40, True)])
+def test_attention_with_another_key_length(it_ctx, B, Sq, Skv, H, D, bf16):
+    """attention(q, k, v, causal=False) with K/V of another sequence length than Q, which the reference accepts
+    (src/ops/attention.rs:304; only the causal branch asserts equal lengths, :349-352), against the oracle; and the
+    causal call with unequal lengths raises the reference's assertion."""
+    from irontensor_b200 import Tensor, attention
+    rng = np.random.default_rng(1000 * Sq + Skv)
+    rnd = lambda *shape: synth.round_bf16(rng.standard_normal(shape).astype(np.float32)) if bf16 else rng.standard_normal(shape).astype(np.float32)
+    q, k, v = rnd(B, Sq, H, D), rnd(B, Skv, H, D), rnd(B, Skv, H, D)
+    mk = Tensor.from_f32_as_bf16 if bf16 else Tensor.from_f32_slice
+    tq, tk, tv = mk(q.reshape(-1), [B, Sq, H, D]), mk(k.reshape(-1), [B, Skv, H, D]), mk(v.reshape(-1), [B, Skv, H, D])
+    out = attention(tq, tk, tv, False)
+    assert it_ctx.poll_status() == 0
+    t = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1, 3))
+    ro, rlse = ol.cross_fwd(t(q), t(k), t(v))
+    got = out.to_f32_host().reshape(B, Sq, H, D).transpose(0, 2, 1, 3)
+    assert np.abs(got - ro).max() <= (BF16_MAX_ABS if bf16 else F32_TOL)
+    assert np.abs(out.lse.to_f32_host().reshape(B, H, Sq) - rlse).max() <= F32_TOL
+    with pytest.raises(AssertionError, match="same seq_len"):
+        attention(tq, tk, tv, True)
+
+
 @pytest.mark.parametrize("S,causal,qk_scale", [(4096, True, 1.0), (4100, True, 1.0), (4225, False, 1.0), (4352, True, 3.0),
                                                (4480, False, 3.0)])
 def test_bf16_long_sequence_forward(it_ctx, S, causal, qk_scale):
