@@ -269,6 +269,49 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     fence_mbar_init();
     fence_proxy_async_smem();
   }
+  // Loads of query tile `qi` of the group's query head `g_` for iteration `n`: Q with the rows' LSE*log2e and delta on
+  // one barrier, dO on another.  Only the producer thread (thread 0) calls it.
+  auto load_q_do = [&](int n, int qi, int g_) -> bool {
+    const int st = n & 1;
+    const uint32_t ph = (n >> 1) & 1;
+    const int hd = hkv * G + g_;   // query head
+    if (!mbar_wait_parked(&q_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return false;
+    mbar_arrive_expect_tx(&q_full[st], T::TILE_BYTES + 1024);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_Q + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[st], b * 64, qi * T::BN, hd, bt);
+    const size_t row0 = static_cast<size_t>(bh0 + g_) * prm.S_pad + static_cast<size_t>(qi) * T::BN;
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(
+            smem_addr(smem + T::SMEM_LSE + st * 512)),
+        "l"(reinterpret_cast<uint64_t>(prm.lse2_pad + row0)), "r"(smem_addr(&q_full[st]))
+        : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(
+            smem_addr(smem + T::SMEM_DELTA + st * 512)),
+        "l"(reinterpret_cast<uint64_t>(prm.delta_pad + row0)), "r"(smem_addr(&q_full[st]))
+        : "memory");
+    if (!mbar_wait_parked(do_empty, (n & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return false;
+    mbar_arrive_expect_tx(do_full, T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_DO + b * T::BLOCK_BYTES, &tmap_do, do_full, b * 64, qi * T::BN, hd, bt);
+    return true;
+  };
+  // The first loads go out before the CTA-wide set-up (tensor-memory allocation, barrier, register hand-over), so
+  // their round trip to memory runs under it: a short-sequence CTA lives for a handful of tiles and this wait is a
+  // visible part of its life.  Nothing is loaded into a CTA that is not going to run.
+  if (threadIdx.x == 0 && *abort_flag == 0 && n_iter > 0) {
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+    prefetch_tensormap(&tmap_do);
+    prefetch_tensormap(&tmap_dq);
+    mbar_arrive_expect_tx(kv_full, 2 * T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b) {
+      tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, hkv, bt);
+      tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, hkv, bt);
+    }
+    load_q_do(0, i0, 0);
+  }
   if (warp == 2) {
     tmem_alloc(tmem_slot, T::TMEM_COLS);
     tmem_relinquish();
@@ -289,46 +332,15 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // nothing to do
     } else if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
+      // (K, V and the first query tile's loads were issued by this thread before the CTA-wide set-up barrier.)
       if (lane == 0) {
-        prefetch_tensormap(&tmap_q);
-        prefetch_tensormap(&tmap_k);
-        prefetch_tensormap(&tmap_v);
-        prefetch_tensormap(&tmap_do);
-        prefetch_tensormap(&tmap_dq);
-        mbar_arrive_expect_tx(kv_full, 2 * T::TILE_BYTES);
-        for (int b = 0; b < T::NBLK; ++b) {
-          tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, hkv, bt);
-          tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, hkv, bt);
-        }
-        int g = 0, qi = i0 - 1;   // query head within the group, query tile
-        for (int n = 0; n < n_iter; ++n) {
-          const int st = n & 1;
-          const uint32_t ph = (n >> 1) & 1;
+        int g = 0, qi = i0;   // query head within the group, query tile (of iteration 0)
+        for (int n = 1; n < n_iter; ++n) {
           if (++qi == n_q_tiles) {
             qi = i0;
             ++g;
           }
-          const int hd = hkv * G + g;   // query head
-          if (!mbar_wait_parked(&q_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
-          mbar_arrive_expect_tx(&q_full[st], T::TILE_BYTES + 1024);
-          for (int b = 0; b < T::NBLK; ++b)
-            tma_load_4d(smem + T::SMEM_Q + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[st], b * 64,
-                        qi * T::BN, hd, bt);
-          const size_t row0 = static_cast<size_t>(bh0 + g) * prm.S_pad + static_cast<size_t>(qi) * T::BN;
-          asm volatile(
-              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(
-                  smem_addr(smem + T::SMEM_LSE + st * 512)),
-              "l"(reinterpret_cast<uint64_t>(prm.lse2_pad + row0)), "r"(smem_addr(&q_full[st]))
-              : "memory");
-          asm volatile(
-              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(
-                  smem_addr(smem + T::SMEM_DELTA + st * 512)),
-              "l"(reinterpret_cast<uint64_t>(prm.delta_pad + row0)), "r"(smem_addr(&q_full[st]))
-              : "memory");
-          if (!mbar_wait_parked(do_empty, (n & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
-          mbar_arrive_expect_tx(do_full, T::TILE_BYTES);
-          for (int b = 0; b < T::NBLK; ++b)
-            tma_load_4d(smem + T::SMEM_DO + b * T::BLOCK_BYTES, &tmap_do, do_full, b * 64, qi * T::BN, hd, bt);
+          if (!load_q_do(n, qi, g)) break;
         }
       }
     } else if (warp == 1) {

@@ -125,6 +125,36 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     fence_mbar_init();
     fence_proxy_async_smem();
   }
+  // Key/value tile j into its ring stage (producer thread only).
+  auto load_kv = [&](int j) -> bool {
+    const int st = j % T::STAGES;
+    const uint32_t ph = (j / T::STAGES) & 1;
+    if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return false;
+    mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64, j * T::BN, hkv, bt);
+    if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return false;
+    mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64, j * T::BN, hkv, bt);
+    return true;
+  };
+  // The query tiles and the first key/value tile go out before the CTA-wide set-up (tensor-memory allocation,
+  // barrier, register hand-over), so their round trip to memory runs under it: at a thousand keys a CTA lives for a
+  // handful of tiles and that wait is a visible part of its life.  Nothing is loaded into a CTA that will not run.
+  if (threadIdx.x == 0 && *abort_flag == 0) {
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+    for (int t = 0; t < 2; ++t) {
+      if (n_kv[t] == 0) continue;
+      mbar_arrive_expect_tx(&q_full[t], T::TILE_BYTES);
+      for (int b = 0; b < T::NBLK; ++b)
+        tma_load_4d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
+                    (2 * pair + t) * T::BM, hd, bt);
+    }
+    if (n_iter > 0) load_kv(0);
+  }
   if (warp == 2) {
     tmem_alloc(tmem_slot, T::TMEM_COLS);
     tmem_relinquish();
@@ -143,31 +173,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // nothing to do
     } else if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
+      // (the query tiles and key/value tile 0 were issued by this thread before the set-up barrier)
       if (lane == 0) {
-        prefetch_tensormap(&tmap_q);
-        prefetch_tensormap(&tmap_k);
-        prefetch_tensormap(&tmap_v);
-        for (int t = 0; t < 2; ++t) {
-          if (n_kv[t] == 0) continue;
-          mbar_arrive_expect_tx(&q_full[t], T::TILE_BYTES);
-          for (int b = 0; b < T::NBLK; ++b)
-            tma_load_4d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
-                        (2 * pair + t) * T::BM, hd, bt);
-        }
-        for (int j = 0; j < n_iter; ++j) {
-          const int st = j % T::STAGES;
-          const uint32_t ph = (j / T::STAGES) & 1;
-          if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
-          mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
-          for (int b = 0; b < T::NBLK; ++b)
-            tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64,
-                        j * T::BN, hkv, bt);
-          if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
-          mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
-          for (int b = 0; b < T::NBLK; ++b)
-            tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64,
-                        j * T::BN, hkv, bt);
-        }
+        for (int j = 1; j < n_iter; ++j)
+          if (!load_kv(j)) break;
       }
     } else if (warp == 1) {
       // ------------------------------------------------------------ MMA issuer (one thread)
