@@ -729,7 +729,7 @@ def run_layer(args, rank, world, local_rank):
     import torch.distributed as dist
     from irontensor_b200 import (Precision, Tensor, attention_packed, attention_packed_backward, context, linear_backward,
                                  linear_forward, qkv_rope_forward, raw)
-    from irontensor_b200.sharding import head_shard, out_projection_all_reduce, qkv_weight_rows
+    from irontensor_b200.sharding import SummedProjection, head_shard, out_projection_all_reduce, qkv_weight_rows
     torch.cuda.set_device(local_rank)
     ctx = context(local_rank)
     peaks = measured_peaks()
@@ -752,14 +752,22 @@ def run_layer(args, rank, world, local_rank):
 
         chunks = max(args.layer_chunks, 1) if world_ > 1 else 1
         rows = n // chunks
+        fused = {}   # result buffers in symmetric memory for the GEMMs that do their own reduce-scatter
+        if world_ > 1:
+            fused["out"], fused["dx"] = SummedProjection(n, hidden), SummedProjection(n, hidden)
 
         def step(reduce):
             """reduce: False = no exchange; True = one blocking all-reduce per sum; "overlap" = the two GEMMs whose results
-            are summed over ranks run in row chunks, each chunk's all-reduce (NCCL's stream) under the next chunk's GEMM."""
+            are summed over ranks run in row chunks, each chunk's all-reduce (NCCL's stream) under the next chunk's GEMM;
+            "fused" = those two GEMMs add their row blocks into the owners' buffers over NVLink themselves
+            (it_linear_scatter_add), followed by an all-gather."""
             qkv = qkv_rope_forward(tx, w_l, hl, hkvl, D, 10000.0, 0, packed=True)
             attn = attention_packed(qkv, hl, hkvl, D, True)
             pending = []
-            if reduce == "overlap":
+            if reduce == "fused":
+                a2 = attn.torch().view(n, hl * D)
+                out = Tensor(fused["out"].run(0, a2.data_ptr(), wo_l.data_ptr(), hl * D, hidden).reshape(-1), [n, hidden], Precision.BF16)
+            elif reduce == "overlap":
                 out = Tensor.empty([n, hidden], Precision.BF16)
                 a2 = attn.torch().view(n, hl * D)
                 for c in range(chunks):
@@ -772,7 +780,12 @@ def run_layer(args, rank, world, local_rank):
                     out_projection_all_reduce(out.torch())
             d_attn, d_wo = linear_backward(tdout, attn.view([n, hl * D]), wo_l)
             d_qkv = attention_packed_backward(d_attn.view([B, S, hl, D]), qkv, attn, hl, hkvl, D, True, rope_base=10000.0)
-            if reduce == "overlap":
+            if reduce == "fused":
+                d_w = Tensor.empty([width, hidden], Precision.FP32)
+                g2, x2 = d_qkv.torch().view(n, width), tx.torch().view(n, hidden)
+                raw.linear_bwd(n, hidden, width, g2.data_ptr(), x2.data_ptr(), w_l.data_ptr(), None, d_w.data_ptr())   # no exchange
+                d_x = Tensor(fused["dx"].run(1, g2.data_ptr(), w_l.data_ptr(), hidden, width).reshape(-1), [n, hidden], Precision.BF16)
+            elif reduce == "overlap":
                 d_x, d_w = Tensor.empty([n, hidden], Precision.BF16), Tensor.empty([width, hidden], Precision.FP32)
                 g2, x2 = d_qkv.torch().view(n, width), tx.torch().view(n, hidden)
                 for c in range(chunks):
@@ -806,28 +819,38 @@ def run_layer(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(fn):
+    def timed_interleaved(fns):
+        """Mean device time per call of each function, the functions taking turns step by step, so that the drift
+        of the clock under the power cap during the run falls on all of them alike.  Max over ranks."""
         for _ in range(warmup):
-            fn()
-        l0 = ctx.launch_count()
+            for fn in fns:
+                fn()
         barrier()
-        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-        for a, b in ev:
-            flush.fill_(1)
-            a.record()
-            fn()
-            b.record()
+        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)] for _ in fns]
+        for i in range(steps):
+            for j, fn in enumerate(fns):
+                flush.fill_(1)
+                ev[j][i][0].record()
+                fn()
+                ev[j][i][1].record()
         barrier()
         ctx.poll_status()
-        return max_over_ranks(sum(a.elapsed_time(b) for a, b in ev) / steps), ctx.launch_count() - l0
+        return [max_over_ranks(sum(a.elapsed_time(b) for a, b in e) / steps) for e in ev]
 
-    ms, launches = timed(lambda: step(True))
-    ms_local, _ = timed(lambda: step(False))              # the same without the two all-reduces
-    ms_overlap = timed(lambda: step("overlap"))[0] if (world > 1 and args.layer_chunks > 0) else None
+    l0 = ctx.launch_count()
+    step(False)
+    launches = ctx.launch_count() - l0
+    if world > 1:
+        ms_nccl, ms_local, ms_fused = timed_interleaved([lambda: step(True), lambda: step(False), lambda: step("fused")])
+        ms = min(ms_nccl, ms_fused)      # the line's value is the faster of the two exchanges; both are reported
+    else:
+        ms = ms_nccl = ms_local = timed_interleaved([lambda: step(False)])[0]
+        ms_fused = None
+    ms_overlap = timed_interleaved([lambda: step("overlap")])[0] if (world > 1 and args.layer_chunks > 0) else None
     buf = torch.empty((n, hidden), dtype=torch.bfloat16, device="cuda")
-    ms_ar, _ = timed(lambda: out_projection_all_reduce(buf)) if world > 1 else (0.0, 0)
+    ms_ar = timed_interleaved([lambda: out_projection_all_reduce(buf)])[0] if world > 1 else 0.0
     # the summed results against the unsharded layer on rank 0 (same seed, same kernels, all heads on one GPU)
-    out, d_x, _, _ = step(True)
+    out, d_x, _, _ = step("fused" if world > 1 else False)      # the fused exchange's result is the one checked
     check = None
     if rank == 0:
         full_step, _, _ = make(1, 0)
@@ -848,16 +871,23 @@ def run_layer(args, rank, world, local_rank):
             "unit": "TFLOP/s", "value": flops / ms / 1e9, "higher_is_better": True, "n_gpus": world, "steps": steps, "warmup": warmup,
             "dtype": "bf16", "data": "synthetic", "ms_per_step": ms, "scaling": "strong",
             "config": {"workload": "attention layer B4 S8192 hidden 2048, 16 heads of 128, packed q|k|v, bf16",
-                       "sharding": f"{hl} of {H} heads per rank; output projection and input gradient summed by NCCL all-reduce",
+                       "sharding": f"{hl} of {H} heads per rank; output projection and input gradient are sums over ranks",
                        "flops": {"projections": 3 * gemm, "attention": 7.0 * B * H * S * S * D}},
+            "exchange": {"used_for_value": None if world == 1 else ("nccl_all_reduce" if ms_nccl <= ms_fused else "fused_reduce_scatter"),
+                         "ms_per_step_nccl_all_reduce": ms_nccl if world > 1 else None,
+                         "ms_per_step_fused_reduce_scatter": ms_fused,
+                         "fused_reduce_scatter": "the two summed GEMMs add their row blocks into the owners' buffers themselves (TMA "
+                                                 "reduce-add over NVLink peer memory in the epilogue), then NCCL all-gather",
+                         "ms_per_step_no_exchange": ms_local, "share_of_step": (ms - ms_local) / ms if world > 1 else 0.0,
+                         "timing": "the three variants take turns step by step (clock drift under the power cap falls on all alike)"},
             "all_reduce": {"per_step": 2 if world > 1 else 0, "bytes_each": ar_bytes, "ms_each_alone": ms_ar,
                            "bus_gbs_alone": (2 * (world - 1) / world * ar_bytes / (ms_ar * 1e-3) / 1e9) if world > 1 else None,
-                           "ms_per_step_without": ms_local, "share_of_step": (ms - ms_local) / ms if world > 1 else 0.0,
+                           "ms_per_step_without": ms_local, "share_of_step": (ms_nccl - ms_local) / ms_nccl if world > 1 else 0.0,
                            "ms_per_step_chunked_overlap": ms_overlap,
                            "chunked_overlap": (f"{args.layer_chunks} row chunks per summed GEMM, each chunk's all-reduce issued under the "
                                                "next chunk's GEMM; slower than one blocking all-reduce: NCCL's kernel cannot run "
                                                "beside a GEMM that holds every SM") if ms_overlap is not None else None},
-            "check": check, "gpu_launches": launches,
+            "check": check, "gpu_launches": launches, "gpu_launches_note": "library kernels of one step without exchange",
             "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9 / world, "peak": peaks["bf16"], "unit": "TFLOP/s",
                          "frac": flops / ms / 1e9 / world / peaks["bf16"], "traffic": None, "note": "per GPU"}}
     print(json.dumps(line), flush=True)

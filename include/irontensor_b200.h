@@ -205,6 +205,23 @@ it_status it_linear_fwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_di
 it_status it_linear_bwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_dim, int32_t out_dim, const void* dy,
                         const void* x, const void* w, void* dx, float* dw);
 
+/* A projection whose result is a SUM OVER GPUs, with the reduce-scatter done by the GEMM itself.  With the heads of a layer
+ * split over `world` GPUs, the output projection (src/train/forward.rs:146: attn [n, heads*D] @ Wo^T) and the gradient of
+ * the layer's input (src/train/backward.rs:139-147) are sums over ranks of partial products; the reference is single-device
+ * and has neither.  kind 0: a [n, in] times W [out, in]^T -> [n, out];  kind 1: a [n, out] times W [out, in] -> [n, in]
+ * (bf16, fp32 accumulation, as it_linear_fwd / the dx of it_linear_bwd).  Instead of storing its partial product the
+ * kernel ADDS row block [r*rows_per_rank, (r+1)*rows_per_rank) into c_of_rank[r] as the tiles leave tensor memory
+ * (TMA reduce-adds of bf16 in whole 128-byte lines, over NVLink for r != this rank), so the exchange runs under the GEMM's own math and after all
+ * ranks' calls rank r holds the finished sum of its row block; an all-gather of the row blocks makes it an all-reduce.
+ * c_of_rank[r]: the [n, width] bf16 result buffer of rank r as a pointer THIS process may store to (peer mapping of a
+ * symmetric allocation; c_of_rank[own rank] is local memory).  The caller zeroes its own row block and synchronises
+ * the ranks before the call (no add may arrive before the zeroing) and after it (all adds have landed) -- with a
+ * collective barrier over the same ranks.  The summed product's width must be a multiple of 64 and rows_per_rank of
+ * 128; world <= 8.  Sums of
+ * bf16 partials are rounded to bf16 at every add, like a bf16 all-reduce. */
+it_status it_linear_scatter_add(it_ctx* ctx, it_stream* stream, int32_t kind, int32_t n, int32_t in_dim, int32_t out_dim,
+                                const void* a, const void* w, void* const* c_of_rank, int32_t world, int32_t rows_per_rank);
+
 /* The Q, K and V projections and the rotary embedding of Q and K as ONE kernel: x [batch*seq, hidden] times the
  * stacked weights w_qkv = [Wq; Wk; Wv] ([(heads + 2*kv_heads)*head_dim, hidden]), the rotation applied in the
  * GEMM's epilogue, q_out [batch, seq, heads, head_dim], k_out and v_out [batch, seq, kv_heads, head_dim] written

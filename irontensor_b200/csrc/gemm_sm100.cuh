@@ -28,8 +28,10 @@ struct GemmTraits {
   static constexpr int A_BYTES = BM * BK * 2;      // 16 KB
   static constexpr int B_BYTES = BN * BK * 2;      // 32 KB
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SMEM_BAR = STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int OUT_BYTES = BM * 128;       // reduce-scatter epilogue: staging of 128 rows x 64 bf16 columns, two of them
+  static constexpr int SMEM_OUT = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BAR = SMEM_OUT + 2 * OUT_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;
   static constexpr int SMEM_MISC = SMEM_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = SMEM_MISC + 16;
   static constexpr int THREADS = 256;
@@ -50,6 +52,17 @@ struct GemmParams {
   long long ld_q, ld_kv;      // elements between the rows (tokens) of q and of k / v: heads*D and kv_heads*D when the three are
                               // separate tensors, (heads + 2 kv_heads)*D when they are column ranges of one packed buffer
   const float2* rope_table;   // [seq][head_dim / 2] (cos, sin), or null: no rotation
+  // Reduce-scatter epilogue (gemm_bf16_sm100_kernel<.., .., true>): row block [r * rs_rows, (r + 1) * rs_rows) of the
+  // product is ADDED into rank r's copy of C, so that after every rank's GEMM rank r holds the sum over ranks of its
+  // row block.  rs_rows is a multiple of the tile height, so a tile has one owner.
+  int rs_world;
+  int rs_rows;
+};
+
+// Tensor maps of every rank's copy of C ([n, width] bf16, boxes of 64 columns x 128 rows) for the reduce-scatter
+// epilogue: this GPU's own memory or a peer's, mapped into this process.
+struct GemmScatterMaps {
+  CUtensorMap c_of_rank[8];
 };
 
 // Tile index -> tile coordinates.  Tiles are numbered in groups of 16 rows of tiles: within a group the M
@@ -73,10 +86,14 @@ __device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tile
 // src/train/forward.rs:101-103,111-112) whose epilogue applies the rotary embedding to the Q and K
 // columns - a rotation pair is two neighbouring accumulator registers of the thread that owns the token's
 // row; cosines and sines come from a table built once per call - and writes q_rope, k_rope and v in the [batch, seq, heads, head_dim] layout attention reads.
-template <int LAYOUT, bool QKV = false>
+// RS = true is the GEMM that does its own reduce-scatter: the epilogue warps round each 128 x 64 piece of a finished
+// tile to bf16 into a swizzled staging buffer, and one thread (warp 3) adds it into the copy of C of the rank that
+// owns those rows with a TMA reduce-add -- whole 128-byte lines, over NVLink when the owner is a peer -- while the
+// tensor core is already on the next tile.
+template <int LAYOUT, bool QKV = false, bool RS = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                       const GemmParams prm) {
+                       const GemmParams prm, const __grid_constant__ GemmScatterMaps rs_maps) {
   using T = GemmTraits;
   using namespace ptx;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -85,6 +102,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   uint64_t* empty = full + T::STAGES;       // [STAGES] MMAs that read the stage are complete
   uint64_t* acc_full = empty + T::STAGES;   // [2] a tile's accumulator is complete
   uint64_t* acc_empty = acc_full + 2;       // [2] the epilogue has read it (128 arrivals)
+  uint64_t* out_full = acc_empty + 2;       // [2] a staging buffer holds a piece (128 arrivals)
+  uint64_t* out_free = out_full + 2;        // [2] the reduce-add has read it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + T::SMEM_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::SMEM_MISC + 4);
 
@@ -107,6 +126,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 128);
+      mbar_init(&out_full[i], 128);
+      mbar_init(&out_free[i], 1);
     }
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -187,10 +208,37 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (ok) umma_commit(&acc_full[buf]);
       }
     }
+  } else if (warp == 3) {
+    if (RS && lane == 0) {
+      // reduce-add issuer: pieces in the order the epilogue produces them
+      int g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        gemm_tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        const int m0 = tm * T::BM, n0 = tn * T::BN;
+        const CUtensorMap* map = &rs_maps.c_of_rank[min(m0 / prm.rs_rows, prm.rs_world - 1)];
+        for (int c = 0; c < T::BN / 64; ++c) {
+          if (n0 + c * 64 >= prm.N) break;        // the epilogue produces no piece past the last column
+          const int buf = g & 1;
+          ok = mbar_wait(&out_full[buf], static_cast<uint32_t>(g >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+          if (!ok) break;
+          tma_reduce_add_4d(map, smem + T::SMEM_OUT + buf * T::OUT_BYTES, n0 + c * 64, m0, 0, 0);
+          bulk_commit_group();
+          if (g >= 1) {   // the previous piece's reduce has read the other buffer: hand it back
+            bulk_wait_group_read<1>();
+            mbar_arrive(&out_free[buf ^ 1]);
+          }
+          ++g;
+        }
+      }
+      bulk_wait_group_all();   // the adds have been performed, at the peers too, before the kernel ends
+    }
   } else if (warp >= 4) {
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     int t = 0;
+    int rs_g = 0;   // staged pieces so far (reduce-scatter epilogue)
     bool ok = true;
     uint32_t r[32];
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
@@ -203,6 +251,41 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + row_in_tile;
+      if (RS) {
+        // 64 columns at a time: this thread's row of the piece is 128 bytes of the staging buffer (128-byte swizzle, the
+        // layout the tensor map of C expects); rows past M and columns past N are dropped by the reduce-add
+        const int swz = row_in_tile & 7;
+#pragma unroll 1
+        for (int c = 0; c < T::BN / 64; ++c) {
+          if (n0 + c * 64 >= prm.N) break;
+          const int obuf = rs_g & 1;
+          ok = mbar_wait(&out_free[obuf], ((static_cast<uint32_t>(rs_g) >> 1) & 1) ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          uint8_t* dst = smem + T::SMEM_OUT + obuf * T::OUT_BYTES + row_in_tile * 128;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            tmem_ld_x32(t_lane + buf * T::BN + c * 64 + h * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              w.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              w.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              w.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + (((h * 4 + v) ^ swz) << 4)) = w;
+            }
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&out_full[obuf]);
+          ++rs_g;
+        }
+        if (!ok) break;
+        tc_fence_before();
+        mbar_arrive(&acc_empty[buf]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < T::BN / 32; ++c) {
         tmem_ld_x32(t_lane + buf * T::BN + c * 32, r);

@@ -397,10 +397,15 @@ struct QkvEpilogue {
   const float2* rope_table;
   long long ld_q, ld_kv;
 };
+struct ScatterEpilogue {
+  void* const* c_of_rank;
+  int world, rows_per_rank;
+};
 
-template <int LAYOUT, bool QKV = false>
+template <int LAYOUT, bool QKV = false, bool RS = false>
 it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const void* a, long long lda, const void* b,
-                      long long ldb, void* c, long long ldc, bool c_is_f32, const QkvEpilogue* epi = nullptr) {
+                      long long ldb, void* c, long long ldc, bool c_is_f32, const QkvEpilogue* epi = nullptr,
+                      const ScatterEpilogue* rs = nullptr) {
   using T = it::GemmTraits;
   CUtensorMap ma, mb;
   it_status st;
@@ -411,7 +416,7 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   if ((st = make_tmap(ctx, &mb, b, 1, 1, b_rows, b_cols, sb, (LAYOUT == 0) ? T::BN : T::BK)) != IT_OK) return st;
   static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
-    IT_CUDA(cudaFuncSetAttribute(it::gemm_bf16_sm100_kernel<LAYOUT, QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    IT_CUDA(cudaFuncSetAttribute(it::gemm_bf16_sm100_kernel<LAYOUT, QKV, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  T::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
   }
@@ -427,6 +432,18 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   p.seq = p.heads = p.kv_heads = p.head_dim = 0;
   p.ld_q = p.ld_kv = 0;
   p.rope_table = nullptr;
+  p.rs_world = 0;
+  p.rs_rows = 1;
+  static const it::GemmScatterMaps no_maps{};
+  it::GemmScatterMaps rs_maps;
+  if (RS) {
+    p.rs_world = rs->world;
+    p.rs_rows = rs->rows_per_rank;
+    const it::TensorStrides sc{ldc, ldc * M, ldc * M, 1};
+    for (int i = 0; i < rs->world; ++i)
+      if ((st = make_tmap(ctx, &rs_maps.c_of_rank[i], rs->c_of_rank[i], 1, 1, M, N, sc, T::BM)) != IT_OK) return st;
+    for (int i = rs->world; i < 8; ++i) rs_maps.c_of_rank[i] = rs_maps.c_of_rank[0];
+  }
   if (epi != nullptr) {
     p.q = static_cast<__nv_bfloat16*>(epi->q);
     p.k = static_cast<__nv_bfloat16*>(epi->k);
@@ -441,7 +458,7 @@ it_status launch_gemm(it_ctx* ctx, cudaStream_t s, int M, int N, int K, const vo
   }
   const int n_tiles = ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
   const int grid = std::min(n_tiles, ctx->sm_count);
-  it::gemm_bf16_sm100_kernel<LAYOUT, QKV><<<grid, T::THREADS, T::SMEM_BYTES, s>>>(ma, mb, p);
+  it::gemm_bf16_sm100_kernel<LAYOUT, QKV, RS><<<grid, T::THREADS, T::SMEM_BYTES, s>>>(ma, mb, p, RS ? rs_maps : no_maps);
   ctx->launches += 1;
   IT_CUDA(cudaGetLastError());
   return IT_OK;
@@ -1023,6 +1040,34 @@ it_status it_linear_fwd(it_ctx* ctx, it_stream* stream, int32_t n, int32_t in_di
   }
   IT_CUDA(cudaSetDevice(ctx->device));
   return launch_gemm<0>(ctx, stream->s, n, out_dim, in_dim, x, in_dim, w, in_dim, y, out_dim, false);
+}
+
+it_status it_linear_scatter_add(it_ctx* ctx, it_stream* stream, int32_t kind, int32_t n, int32_t in_dim, int32_t out_dim,
+                                const void* a, const void* w, void* const* c_of_rank, int32_t world, int32_t rows_per_rank) {
+  it_status st = check_linear(ctx, stream, n, in_dim, out_dim);
+  if (st != IT_OK) return st;
+  if (kind != 0 && kind != 1) return fail(IT_ERR_INVALID_ARG, "kind must be 0 (a W^T) or 1 (a W)");
+  if (world < 1 || world > 8) return fail(IT_ERR_INVALID_ARG, "world must be in 1..8, got %d", world);
+  if (rows_per_rank < 1 || static_cast<int64_t>(rows_per_rank) * world < n)
+    return fail(IT_ERR_INVALID_ARG, "rows_per_rank * world must cover the %d rows", n);
+  if (c_of_rank == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  // kind 0: a [n, in] W [out, in] -> [n, out];  kind 1: a [n, out] W [out, in] -> [n, in]
+  const int k_dim = kind == 0 ? in_dim : out_dim, c_cols = kind == 0 ? out_dim : in_dim;
+  if (n == 0 || c_cols == 0 || k_dim == 0) return IT_OK;   // nothing to add
+  if (c_cols % 64 != 0 || rows_per_rank % 128 != 0)
+    return fail(IT_ERR_UNSUPPORTED_SHAPE,
+                "the summed product's width must be a multiple of 64 and rows_per_rank a multiple of 128, got %d and %d", c_cols,
+                rows_per_rank);
+  if (a == nullptr || w == nullptr) return fail(IT_ERR_INVALID_ARG, "null tensor");
+  if (!aligned16(a) || !aligned16(w)) return fail(IT_ERR_ALIGNMENT, "tensors must be 16-byte aligned");
+  for (int r = 0; r < world; ++r) {
+    if (c_of_rank[r] == nullptr) return fail(IT_ERR_INVALID_ARG, "null result pointer for rank %d", r);
+    if (!aligned16(c_of_rank[r])) return fail(IT_ERR_ALIGNMENT, "result pointers must be 16-byte aligned");
+  }
+  IT_CUDA(cudaSetDevice(ctx->device));
+  const ScatterEpilogue rs{c_of_rank, world, rows_per_rank};
+  return kind == 0 ? launch_gemm<0, false, true>(ctx, stream->s, n, out_dim, in_dim, a, in_dim, w, in_dim, nullptr, out_dim, false, nullptr, &rs)
+                   : launch_gemm<1, false, true>(ctx, stream->s, n, in_dim, out_dim, a, out_dim, w, in_dim, nullptr, in_dim, false, nullptr, &rs);
 }
 
 it_status it_qkv_rope_workspace_bytes(int32_t S, int32_t D, size_t* out_bytes) {

@@ -379,6 +379,15 @@ class raw:
         _lib.check(c.lib.it_linear_bwd(c.handle, c.stream(), n, in_dim, out_dim, dy, x, w, dx, dw))
 
     @staticmethod
+    def linear_scatter_add(kind, n, in_dim, out_dim, a, w, c_of_rank, rows_per_rank, ctx=None):
+        """kind 0: a W^T, kind 1: a W; row block r of the product is added into c_of_rank[r] (device pointers this
+        process may store to, one per rank).  See it_linear_scatter_add."""
+        c = ctx or context()
+        arr = (ctypes.c_void_p * len(c_of_rank))(*[int(p) for p in c_of_rank])
+        _lib.check(c.lib.it_linear_scatter_add(c.handle, c.stream(), kind, n, in_dim, out_dim, a, w, arr, len(c_of_rank),
+                                               rows_per_rank))
+
+    @staticmethod
     def bwd_workspace_bytes(dtype, B, H, S, D):
         n = ctypes.c_size_t()
         _lib.check(_lib.load().it_flash_attention_bwd_workspace_bytes(dtype, B, H, S, D, ctypes.byref(n)))

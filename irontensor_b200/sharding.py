@@ -45,3 +45,42 @@ def out_projection_all_reduce(partial, group=None):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
     return partial
+
+
+class SummedProjection:
+    """A projection whose result is a sum over the ranks, with the reduce-scatter fused into the GEMM.
+
+    Owns one [n, width] bf16 result buffer in symmetric memory (every rank allocates the same, and each can store
+    into the others' over NVLink).  run() zeroes this rank's row block, meets the other ranks, runs the GEMM whose
+    epilogue adds every row block of the partial product straight into its owner's buffer (it_linear_scatter_add: the
+    exchange proceeds tile by tile under the GEMM's own math), meets the ranks again, and all-gathers the finished
+    row blocks (NCCL), so that every rank ends with the full sum like out_projection_all_reduce -- at the price of
+    one all-gather instead of an all-reduce after the GEMM.  n must be a multiple of the world size."""
+
+    def __init__(self, n, width, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if n % self.world:
+            raise ValueError("the number of rows must be a multiple of the world size")
+        self.n, self.width, self.rows = n, width, n // self.world
+        self.buf = symm.empty((n, width), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.buf, self.group)
+        self.peers = [int(p) for p in self.handle.buffer_ptrs]
+        self.own = self.buf[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def run(self, kind, a_ptr, w_ptr, in_dim, out_dim, gather=True):
+        """kind 0: a [n, in] W[out, in]^T (width = out); kind 1: a [n, out] W [out, in] (width = in).  Returns the buffer
+        (full sum on every rank), or with gather=False this rank's finished row block only."""
+        import torch.distributed as dist
+        from . import raw
+        self.own.zero_()
+        self.handle.barrier()          # nobody adds into a block that is not zeroed yet
+        raw.linear_scatter_add(kind, self.n, in_dim, out_dim, a_ptr, w_ptr, self.peers, self.rows)
+        self.handle.barrier()          # every rank's adds have landed
+        if not gather:
+            return self.own
+        dist.all_gather_into_tensor(self.buf, self.own, group=self.group)
+        return self.buf
