@@ -33,16 +33,18 @@
 
 namespace it {
 
-template <int D>
+// KT: key tiles a CTA owns (1, or 2 at head_dim 64 where tensor memory has room for two dV and two dK accumulators).
+template <int D, int KT = 1>
 struct BwdTraits {
-  static constexpr int BM = 128;   // keys per CTA tile (TMEM lanes)
+  static_assert(KT == 1 || (KT == 2 && D == 64), "two key tiles per CTA need four accumulators of D columns beside S^T and dP^T");
+  static constexpr int BM = 128;   // keys per tile (TMEM lanes)
   static constexpr int BN = 128;   // query rows per inner tile
   static constexpr int TILE_BYTES = 128 * D * 2;
   static constexpr int BLOCK_BYTES = 128 * 128;
   static constexpr int NBLK = D / 64;
-  static constexpr int SMEM_K = 0;
-  static constexpr int SMEM_V = SMEM_K + TILE_BYTES;
-  static constexpr int SMEM_Q = SMEM_V + TILE_BYTES;        // 2 stages
+  static constexpr int SMEM_K = 0;                          // KT tiles
+  static constexpr int SMEM_V = SMEM_K + KT * TILE_BYTES;   // KT tiles
+  static constexpr int SMEM_Q = SMEM_V + KT * TILE_BYTES;   // 2 stages
   static constexpr int SMEM_DO = SMEM_Q + 2 * TILE_BYTES;   // 1 stage: dO(n) is free again well before dP^T(n+1)
   static constexpr int SMEM_DS = SMEM_DO + TILE_BYTES;      // [2 blocks][128 keys][64 q] bf16
   static constexpr int SMEM_DQS = SMEM_DS + 2 * BLOCK_BYTES;   // dQ staging: [2][128 rows][32 fp32], 128B swizzle
@@ -54,6 +56,7 @@ struct BwdTraits {
   static constexpr int SMEM_BYTES = SMEM_MISC + 16;
   static constexpr int THREADS = 512;
   static constexpr uint32_t TMEM_COLS = 512;
+  // dV and dK of the CTA's key tile t sit at COL_DV + t * D and COL_DK + t * D
   static constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DQ = 128, COL_DV = 256, COL_DK = 384;
 };
 
@@ -191,13 +194,13 @@ __global__ void fa_bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bf
 }
 
 // ------------------------------------------------------------------ (2) main kernel
-template <int D>
+template <int D, int KT = 1>
 __global__ void __launch_bounds__(512, 1)
 fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                     const __grid_constant__ CUtensorMap tmap_dq, const BwdParams prm,
                     const __grid_constant__ RopeFreqs freqs) {
-  using T = BwdTraits<D>;
+  using T = BwdTraits<D, KT>;
   using namespace ptx;
   extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -232,12 +235,31 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // reference's repeat_kv_backward pass, src/shaders/repeat_kv.metal:49-88, does not exist here).
   const int G = prm.st_kv.group;
   const int kv_heads = prm.st.heads / G;
-  int bhk, kt;   // batch * kv_heads + kv_head, key tile
-  grouped_tile_order(static_cast<int>(blockIdx.x), n_k_tiles, static_cast<int>(gridDim.x) / n_k_tiles, &bhk, &kt);
+  // With KT = 2 the CTA owns the key tiles 2*ktp and 2*ktp + 1 (the second may not exist): half as many CTAs, and so
+  // half as many start-ups and epilogues, for the same work -- at a thousand keys those are half of a CTA's life.
+  const int n_kp = (n_k_tiles + KT - 1) / KT;
+  int bhk, ktp;   // batch * kv_heads + kv_head, index of the CTA's key tiles
+  grouped_tile_order(static_cast<int>(blockIdx.x), n_kp, static_cast<int>(gridDim.x) / n_kp, &bhk, &ktp);
+  const int kt = ktp * KT;                                    // first key tile
+  const int nk_cta = min(KT, n_k_tiles - kt);                 // key tiles this CTA owns
   const int hkv = bhk % kv_heads, bt = bhk / kv_heads;        // TMA coordinates of the K/V slice
   const int bh0 = bt * prm.st.heads + hkv * G;                // first query slice of the group
   const int i0 = prm.causal ? kt : 0;
-  const int n_iter = (n_q_tiles - i0) * G;                    // query tiles of every query head of the group
+  // An iteration = (query head of the group, query tile, one of the CTA's key tiles), in that nesting; under the causal
+  // mask key tile kt + t takes part from query tile kt + t on.
+  const int per_head = prm.causal ? (n_q_tiles - kt) * nk_cta - (nk_cta * (nk_cta - 1)) / 2 : n_q_tiles * nk_cta;
+  const int n_iter = per_head * G;
+  // (g, qi, t) of the next iteration; every role walks the same sequence, starting at (0, i0, 0)
+  auto advance = [&](int& g_, int& qi_, int& t_) {
+    ++t_;
+    if (t_ >= nk_cta || (prm.causal && qi_ < kt + t_)) {
+      t_ = 0;
+      if (++qi_ == n_q_tiles) {
+        qi_ = i0;
+        ++g_;
+      }
+    }
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -305,11 +327,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     prefetch_tensormap(&tmap_v);
     prefetch_tensormap(&tmap_do);
     prefetch_tensormap(&tmap_dq);
-    mbar_arrive_expect_tx(kv_full, 2 * T::TILE_BYTES);
-    for (int b = 0; b < T::NBLK; ++b) {
-      tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, kt * T::BM, hkv, bt);
-      tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, kt * T::BM, hkv, bt);
-    }
+    mbar_arrive_expect_tx(kv_full, nk_cta * 2 * T::TILE_BYTES);
+    for (int t = 0; t < nk_cta; ++t)
+      for (int b = 0; b < T::NBLK; ++b) {
+        tma_load_4d(smem + T::SMEM_K + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, kv_full, b * 64, (kt + t) * T::BM, hkv, bt);
+        tma_load_4d(smem + T::SMEM_V + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, kv_full, b * 64, (kt + t) * T::BM, hkv, bt);
+      }
     load_q_do(0, i0, 0);
   }
   if (warp == 2) {
@@ -334,13 +357,10 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // ------------------------------------------------------------ TMA producer
       // (K, V and the first query tile's loads were issued by this thread before the CTA-wide set-up barrier.)
       if (lane == 0) {
-        int g = 0, qi = i0;   // query head within the group, query tile (of iteration 0)
+        int g = 0, qi = i0, t = 0;   // iteration 0
         for (int n = 1; n < n_iter; ++n) {
-          if (++qi == n_q_tiles) {
-            qi = i0;
-            ++g;
-          }
-          if (!load_q_do(n, qi, g)) break;
+          advance(g, qi, t);
+          if (!load_q_do(n, qi, g)) break;   // (with two key tiles a query tile is fetched once per key tile; the second comes from L2)
         }
       }
     } else if (warp == 1) {
@@ -360,8 +380,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // gap in the MMA stream.  Every burst therefore runs `mid` half-way through: a non-blocking probe
         // of the barrier the NEXT burst depends on, whose answer is read when this burst has been issued.
         auto none = [] {};
-        auto issue_st = [&](int st, auto mid) {   // S^T = K * Q^T
-          const uint64_t da = make_sdesc(k_addr, 16, 1024);
+        auto issue_st = [&](int st, int t, auto mid) {   // S^T = K * Q^T   (t: which of the CTA's key tiles)
+          const uint64_t da = make_sdesc(k_addr + t * T::TILE_BYTES, 16, 1024);
           const uint64_t db = make_sdesc(q_addr + st * T::TILE_BYTES, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
@@ -371,8 +391,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
           umma_commit(st_full);
         };
-        auto issue_dpt = [&](auto mid) {   // dP^T = V * dO^T
-          const uint64_t da = make_sdesc(v_addr, 16, 1024);
+        auto issue_dpt = [&](int t, auto mid) {   // dP^T = V * dO^T
+          const uint64_t da = make_sdesc(v_addr + t * T::TILE_BYTES, 16, 1024);
           const uint64_t db = make_sdesc(do_addr, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
@@ -382,28 +402,28 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
           umma_commit(dpt_full);
         };
-        auto issue_dv = [&](bool first, auto mid) {   // dV += P^T * dO   (A from TMEM, B = dO N-major)
+        auto issue_dv = [&](int t, bool first, auto mid) {   // dV += P^T * dO   (A from TMEM, B = dO N-major)
           const uint64_t db = make_sdesc(do_addr, T::BLOCK_BYTES, 1024);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             if (kk == 4) mid();
-            umma_ts(tmem_base + T::COL_DV, tmem_base + T::COL_ST + (kk >> 2) * 64 + (kk & 3) * 8,
+            umma_ts(tmem_base + T::COL_DV + t * D, tmem_base + T::COL_ST + (kk >> 2) * 64 + (kk & 3) * 8,
                     sdesc_advance(db, kk * 2048), IDESC_ND, (!first || kk > 0) ? 1u : 0u);
           }
         };
-        auto issue_dk = [&](int st, bool first, auto mid) {   // dK += dS^T * Q   (A = dS^T K-major, B = Q N-major)
+        auto issue_dk = [&](int st, int t, bool first, auto mid) {   // dK += dS^T * Q   (A = dS^T K-major, B = Q N-major)
           const uint64_t da = make_sdesc(ds_addr, 16, 1024);
           const uint64_t db = make_sdesc(q_addr + st * T::TILE_BYTES, T::BLOCK_BYTES, 1024);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             if (kk == 4) mid();
-            umma_ss(tmem_base + T::COL_DK, sdesc_advance(da, kmajor_off(kk)), sdesc_advance(db, kk * 2048), IDESC_ND,
+            umma_ss(tmem_base + T::COL_DK + t * D, sdesc_advance(da, kmajor_off(kk)), sdesc_advance(db, kk * 2048), IDESC_ND,
                     (!first || kk > 0) ? 1u : 0u);
           }
         };
-        auto issue_dq = [&]() {   // dQ = dS * K   (A = dS M-major from the same buffer, B = K N-major)
+        auto issue_dq = [&](int t) {   // dQ = dS * K   (A = dS M-major from the same buffer, B = K N-major)
           const uint64_t da = make_sdesc(ds_addr, T::BLOCK_BYTES, 1024);
-          const uint64_t db = make_sdesc(k_addr, T::BLOCK_BYTES, 1024);
+          const uint64_t db = make_sdesc(k_addr + t * T::TILE_BYTES, T::BLOCK_BYTES, 1024);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             umma_ss(tmem_base + T::COL_DQ, sdesc_advance(da, kk * 2048), sdesc_advance(db, kk * 2048), IDESC_DQ,
@@ -416,10 +436,16 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (ok) ok = mbar_wait_parked(&q_full[0], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
         if (ok) {
           tc_fence_after();
-          issue_st(0, none);
+          issue_st(0, 0, none);
         }
         bool r_do = false, r_dq = false, r_p = false, r_q = false, r_ds = false;   // answers of the early probes
+        int g_c = 0, qi_c = i0, t_c = 0;     // this iteration's query head, query tile and key tile
+        bool started[KT] = {};               // has the key tile's dV / dK accumulation begun?
         for (int n = 0; n < n_iter && ok; ++n) {
+          const int t = t_c;
+          advance(g_c, qi_c, t_c);           // t_c: the next iteration's key tile
+          const bool first = !started[t];
+          started[t] = true;
           const int st = n & 1;
           const uint32_t par = n & 1;
           const bool more = (n + 1 < n_iter);
@@ -430,25 +456,25 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (ok && n > 0) ok = need(r_dq, dq_empty, (n - 1) & 1, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
-          issue_dpt([&] { r_p = mbar_test_wait(p_full, par); });
+          issue_dpt(t, [&] { r_p = mbar_test_wait(p_full, par); });
           ok = need(r_p, p_full, par, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
-          issue_dv(n == 0, [&] { r_q = more && mbar_test_wait(&q_full[st_n], ph_n); });
+          issue_dv(t, first, [&] { r_q = more && mbar_test_wait(&q_full[st_n], ph_n); });
           umma_commit(do_empty);
           r_ds = false;
           if (more) {
             ok = need(r_q, &q_full[st_n], ph_n, DEV_ERR_TIMEOUT_LOAD);
             if (!ok) break;
             tc_fence_after();
-            issue_st(st_n, [&] { r_ds = mbar_test_wait(ds_full, par); });
+            issue_st(st_n, t_c, [&] { r_ds = mbar_test_wait(ds_full, par); });
           }
           ok = need(r_ds, ds_full, par, DEV_ERR_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
-          issue_dq();
+          issue_dq(t);
           umma_commit(dq_full);
-          issue_dk(st, n == 0, [&] {
+          issue_dk(st, t, first, [&] {
             r_do = more && mbar_test_wait(do_full, par ^ 1);
             r_dq = more && mbar_test_wait(dq_empty, par);
           });
@@ -464,12 +490,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (lane == 0) {
         bool ok = true;
         int g = 0;
-        int qi = i0 - 1, bh_q = bh0;
-        for (int n = 0; n < n_iter && ok; ++n) {
-          if (++qi == n_q_tiles) {
-            qi = i0;
-            ++bh_q;
-          }
+        int g_q = 0, qi = i0, t_q = 0;
+        for (int n = 0; n < n_iter && ok; ++n, advance(g_q, qi, t_q)) {
+          const int bh_q = bh0 + g_q;
 #pragma unroll
           for (int c = 0; c < D / 32; ++c, ++g) {
             const int buf = g & 1;
@@ -494,7 +517,6 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int half = (warp - 4) >> 2;                 // which 64 of the 128 query columns
       const int lane_base = (warp & 3) * 32;
       const int k_local = lane_base + lane;
-      const int k_row = kt * T::BM + k_local;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
       const uint32_t t_st = t_lane + T::COL_ST + half * 64;
       const uint32_t t_dpt = t_lane + T::COL_DPT + half * 64;
@@ -504,11 +526,10 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = true;
       uint32_t ra[16], rb[16];
       uint32_t p_keep[32];   // this thread's 64 P^T values, packed bf16, kept between the two phases
-      int qi = i0 - 1;
-      for (int n = 0; n < n_iter; ++n) {
+      int g_m = 0, qi = i0, t_m = 0;
+      for (int n = 0; n < n_iter; ++n, advance(g_m, qi, t_m)) {
         const int st = n & 1;
-        if (++qi == n_q_tiles) qi = i0;
-        const bool diag = prm.causal && (qi == kt);
+        const bool diag = prm.causal && (qi == kt + t_m);   // the key tile's own query tile: keys after the query are masked
         const float* lse_s = reinterpret_cast<const float*>(smem + T::SMEM_LSE + st * 512) + half * 64;
         const float* dl_s = reinterpret_cast<const float*>(smem + T::SMEM_DELTA + st * 512) + half * 64;
         // lse/delta for this query tile ride on the Q barrier
@@ -597,12 +618,14 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // each math group writes one half of the head dimension of its key row's dV and dK
         tc_fence_after();
         constexpr int HC = D / 2;
-        const long long out_off = prm.st_kv.slice(bh0) + static_cast<long long>(k_row) * prm.st_kv.row + half * HC;
-        __nv_bfloat16* dv_row = prm.dv + out_off;
-        __nv_bfloat16* dk_row = prm.dk + out_off;
 #pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
-          const uint32_t col = (which ? T::COL_DK : T::COL_DV) + half * HC;
+        for (int tw = 0; tw < 2 * nk_cta; ++tw) {   // dV then dK of each of the CTA's key tiles
+          const int t = tw >> 1, which = tw & 1;
+          const int k_row = (kt + t) * T::BM + k_local;
+          const long long out_off = prm.st_kv.slice(bh0) + static_cast<long long>(k_row) * prm.st_kv.row + half * HC;
+          __nv_bfloat16* dv_row = prm.dv + out_off;
+          __nv_bfloat16* dk_row = prm.dk + out_off;
+          const uint32_t col = (which ? T::COL_DK : T::COL_DV) + t * D + half * HC;
           const float f = which ? prm.scale : 1.0f;
           __nv_bfloat16* orow = which ? dk_row : dv_row;
 #pragma unroll 1

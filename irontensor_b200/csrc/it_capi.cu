@@ -336,7 +336,11 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   }
   static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
   if (!attr_set[ctx->device & 15]) {
-    IT_CUDA(cudaFuncSetAttribute(it::fa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    IT_CUDA(cudaFuncSetAttribute(it::fa_bwd_sm100_kernel<D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 it::BwdTraits<D, 1>::SMEM_BYTES));
+    if constexpr (D == 64)
+      IT_CUDA(cudaFuncSetAttribute(it::fa_bwd_sm100_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   it::BwdTraits<D, 2>::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
   }
   float* dq_accum = reinterpret_cast<float*>(ws + w.dq_accum_off);
@@ -364,12 +368,25 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   const int n_kt = (S + 127) / 128;
+  // At head_dim 64 a CTA can own two key tiles (tensor memory holds four accumulators of 64 columns): half as many
+  // CTAs, so half as many start-ups and epilogues for the same work.  Taken when the launch has CTAs to spare (more
+  // than two per SM with one key tile each); a launch that does not even fill the GPU is a latency case and keeps
+  // the shorter CTAs.  IT_BWD_KEY_TILES=1 or 2 in the environment overrides the choice (the tests run both forms).
+  const char* force = getenv("IT_BWD_KEY_TILES");
+  const bool two_tiles = (D == 64) && n_kt >= 2 &&
+                         (force != nullptr ? force[0] == '2' : static_cast<long long>(n_kt) * B * Hkv > 2LL * ctx->sm_count);
   if (ctx->timing >= 2) {
     IT_CUDA(cudaEventRecord(ctx->ev[2][1], s));
     ctx->ev_valid[2] = true;
   }
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
-  it::fa_bwd_sm100_kernel<D><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p, rf);
+  if constexpr (D == 64) {
+    if (two_tiles)
+      it::fa_bwd_sm100_kernel<D, 2><<<static_cast<unsigned>((n_kt + 1) / 2) * B * Hkv, T::THREADS, it::BwdTraits<D, 2>::SMEM_BYTES, s>>>(
+          mq, mk, mv, mdo, mdq, p, rf);
+  }
+  if (!two_tiles)
+    it::fa_bwd_sm100_kernel<D, 1><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p, rf);
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
