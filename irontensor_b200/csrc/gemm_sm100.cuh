@@ -251,7 +251,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + row_in_tile;
-      if (RS) {
+      if constexpr (RS) {
         // 64 columns at a time: this thread's row of the piece is 128 bytes of the staging buffer (128-byte swizzle, the
         // layout the tensor map of C expects); rows past M and columns past N are dropped by the reduce-add
         const int swz = row_in_tile & 7;
@@ -282,10 +282,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           ++rs_g;
         }
         if (!ok) break;
-        tc_fence_before();
-        mbar_arrive(&acc_empty[buf]);
-        continue;
-      }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < T::BN / 32; ++c) {
         tmem_ld_x32(t_lane + buf * T::BN + c * 32, r);
@@ -366,6 +363,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             }
           }
         }
+      }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);

@@ -23,6 +23,7 @@
 #include "fa_fwd_sm100.cuh"
 #include "fa_decode.cuh"
 #include "fa_fwd_pp_sm100.cuh"
+#include "fa_fwd_f32_sm100.cuh"
 #include "gemm_sm100.cuh"
 #include "fa_generic.cuh"
 #include "selftest_sm100.cuh"
@@ -163,6 +164,33 @@ it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, 
                         const void* v, void* o, float* lse, const it::TensorStrides& st, const it::TensorStrides& skv,
                         int Skv = -1) {
   if (Skv < 0) Skv = S;   // self-attention; a different key/value length only comes from it_attention_cross_fwd
+  if (sizeof(ST) == 4 && D <= 64 && (D & 3) == 0 && S >= 128 && Skv == S && getenv("IT_F32_CUDA_CORES") == nullptr) {
+    // fp32 tensors with at least one full 128-row tile: the tensor-core kernel (operands split into three bf16 terms).
+    // Shorter sequences -- the per-token calls of generation without a key/value cache -- stay on the latency kernel below.
+    using T = it::FwdF32Traits;
+    static std::atomic<bool> attr_set[16];
+    if (!attr_set[ctx->device & 15]) {
+      IT_CUDA(cudaFuncSetAttribute(it::fa_fwd_f32_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+      attr_set[ctx->device & 15] = true;
+    }
+    it::FwdF32Params p;
+    p.q = static_cast<const float*>(q);
+    p.k = static_cast<const float*>(k);
+    p.v = static_cast<const float*>(v);
+    p.o = static_cast<float*>(o);
+    p.lse = lse;
+    p.st = st;
+    p.st_kv = skv;
+    p.status = ctx->d_status;
+    p.S = S;
+    p.D = D;
+    p.causal = causal;
+    p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
+    it::fa_fwd_f32_sm100_kernel<<<static_cast<unsigned>(BH) * ((S + 127) / 128), T::THREADS, T::SMEM_BYTES, s>>>(p);
+    ctx->launches += 1;
+    IT_CUDA(cudaGetLastError());
+    return IT_OK;
+  }
   const float scale = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;   // exp2 domain
   const dim3 grid((S + 63) / 64, BH);
   const ST *qq = static_cast<const ST*>(q), *kk = static_cast<const ST*>(k), *vv = static_cast<const ST*>(v);
