@@ -237,25 +237,26 @@ __global__ void __launch_bounds__(288, 1) fa_fwd_f32_sm100_kernel(const FwdF32Pa
     const int k_limit = prm.causal ? min(S - 1, q_row) : (S - 1);   // last visible key index
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
-    uint32_t r[128];
+    uint32_t r[32];   // 32 columns of this thread's row at a time: two passes over S (maximum, then P) keep the code small
     for (int j = 0; j < n_kv; ++j) {
       ok = mbar_wait(s_full, j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      const bool edge = (prm.causal && j == qt) || ((j + 1) * T::BN > S);   // diagonal or ragged last tile
+      const int vis = edge ? k_limit - j * T::BN : 127;                     // columns 0..vis are visible
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_x32(t_lane + T::COL_S + c * 32, r);
+        tmem_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x32(t_lane + T::COL_S + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-      tmem_wait_ld();
-      if ((prm.causal && j == qt) || ((j + 1) * T::BN > S)) {   // diagonal or ragged last tile
-        const int vis = k_limit - j * T::BN;                    // columns 0..vis are visible
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i > vis) r[i] = 0xFF800000u;
+        for (int i = 0; i < 32; i += 2) {
+          const float a0 = (c * 32 + i <= vis) ? __uint_as_float(r[i]) : -INFINITY;
+          const float a1 = (c * 32 + i + 1 <= vis) ? __uint_as_float(r[i + 1]) : -INFINITY;
+          mx = fmax3(mx, a0, a1);
+        }
       }
-      float mx = __uint_as_float(r[0]);
-#pragma unroll
-      for (int i = 1; i < 127; i += 2) mx = fmax3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-      mx = fmaxf(mx, __uint_as_float(r[127]));
       float m_new = mx * sl2;
       if (m_new == -INFINITY) m_new = 0.f;   // a row past S: nothing visible, keep everything finite
       if (j > 0) {   // P(j-1) V(j-1) must be complete before O is rescaled or the P planes are rewritten
@@ -285,13 +286,17 @@ __global__ void __launch_bounds__(288, 1) fa_fwd_f32_sm100_kernel(const FwdF32Pa
       // P = 2^(s*c - m) in fp32, summed in fp32, handed to the tensor core as three bf16 planes
       const float neg_m = -m_used;
       float l0 = 0.f, l1 = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t ph[16], pm[16], pl[16];
+        tmem_ld_x32(t_lane + T::COL_S + c * 32, r);
+        tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(r[c * 32 + i]), sl2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(r[c * 32 + i + 1]), sl2, neg_m));
+          float p0 = ex2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+          float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sl2, neg_m));
+          if (c * 32 + i > vis) p0 = 0.f;
+          if (c * 32 + i + 1 > vis) p1 = 0.f;
           l0 += p0;
           l1 += p1;
           split3_bf16x2(p0, p1, &ph[i >> 1], &pm[i >> 1], &pl[i >> 1]);
@@ -312,17 +317,21 @@ __global__ void __launch_bounds__(288, 1) fa_fwd_f32_sm100_kernel(const FwdF32Pa
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.0f / l_sum;
+      float* orow = prm.o + prm.st.slice(bh) + static_cast<long long>(q_row) * prm.st.row;
+#pragma unroll 1
+      for (int c = 0; c < T::DP / 32; ++c) {
+        tmem_ld_x32(t_lane + T::COL_O + c * 32, r);
+        tmem_wait_ld();
+        if (q_row < S) {
 #pragma unroll
-      for (int c = 0; c < T::DP / 32; ++c) tmem_ld_x32(t_lane + T::COL_O + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-      tmem_wait_ld();
+          for (int c4 = 0; c4 < 8; ++c4)
+            if (c * 32 + c4 * 4 < D)
+              reinterpret_cast<float4*>(orow)[c * 8 + c4] =
+                  make_float4(__uint_as_float(r[c4 * 4]) * inv_l, __uint_as_float(r[c4 * 4 + 1]) * inv_l,
+                              __uint_as_float(r[c4 * 4 + 2]) * inv_l, __uint_as_float(r[c4 * 4 + 3]) * inv_l);
+        }
+      }
       if (q_row < S) {
-        float* orow = prm.o + prm.st.slice(bh) + static_cast<long long>(q_row) * prm.st.row;
-#pragma unroll
-        for (int c4 = 0; c4 < T::DP / 4; ++c4)
-          if (c4 * 4 < D)
-            reinterpret_cast<float4*>(orow)[c4] =
-                make_float4(__uint_as_float(r[c4 * 4]) * inv_l, __uint_as_float(r[c4 * 4 + 1]) * inv_l,
-                            __uint_as_float(r[c4 * 4 + 2]) * inv_l, __uint_as_float(r[c4 * 4 + 3]) * inv_l);
         if (prm.lse != nullptr) prm.lse[static_cast<size_t>(bh) * S + q_row] = (m_used + lg2(l_sum)) * 0.6931471805599453f;
       }
     }
