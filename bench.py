@@ -603,6 +603,7 @@ def secondary_configs(ctx, peaks):
     sample: C1 (fp32 forward latency and achieved HBM rate), C2 and C3 (bf16 forward + backward), C5 (per-call
     latency of the 100-call greedy pattern in a CUDA graph)."""
     import torch
+    ctx.enable_kernel_timing(0)     # the event records around the main kernels cost microseconds: visible on these shapes
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     gpu = torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else \
         os.environ["CUDA_VISIBLE_DEVICES"].split(",")[torch.cuda.current_device()]
