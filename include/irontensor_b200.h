@@ -26,6 +26,7 @@ extern "C" {
 typedef struct it_ctx it_ctx;       /* one per process and GPU; stands in for MetalContext (src/device.rs:10-37) */
 typedef struct it_stream it_stream; /* ordered work queue; stands in for a thread's CommandBatch (src/command_batch.rs:49-53) */
 typedef struct it_event it_event;   /* completion marker; stands in for the async command buffer handle (src/command_batch.rs:228-275) */
+typedef struct it_host_step it_host_step; /* buffers and streams of it_host_step_run */
 
 typedef int32_t it_status;
 enum {
@@ -251,6 +252,26 @@ it_status it_attention_packed_bwd(it_ctx* ctx, it_stream* stream, it_dtype dtype
                                   int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t causal, float rope_base,
                                   int32_t position_offset, const void* qkv, const void* o, const void* d_o,
                                   const float* lse, void* dqkv, void* workspace, size_t workspace_bytes);
+
+/* Forward + backward for tensors that live in page-locked HOST memory (the reference's buffers are unified memory, so
+ * its ops never copy: src/tensor.rs:73; on a discrete GPU a caller with host data pays the host link both ways).  One
+ * call enqueues the whole step: the (batch x head) slices are taken `group_slices` at a time, each group on one of
+ * `n_streams` streams in rotation: upload q, k, v, dO -> it_flash_attention_fwd -> it_flash_attention_bwd -> download
+ * o, dq, dk, dv (and lse when hlse is not null), so that one group's upload, another's kernels and a third's download run
+ * at the same time on the two copy engines and the SMs.  With the loop inside the library the host spends microseconds
+ * per group, so groups can be small and the first upload and last download, which nothing overlaps, short.
+ * it_host_step_create allocates the device buffers (per stream: eight group-sized tensors, lse and the backward's
+ * workspace), streams and events once; it_host_step_run allocates nothing.  All host pointers: [n_slices, S, D]
+ * (lse [n_slices, S]) of the dtype given at creation, page-locked (it_host_alloc) for the copies to overlap.  The groups
+ * start after the work enqueued on `stream` so far, and `stream` continues after the last download; nothing is waited
+ * for on the host: it_stream_sync(stream) before reading the results (it reports a device time-out).  copies_only != 0
+ * enqueues the same copies without the kernels (what the host link alone costs).  One run at a time per it_host_step. */
+it_status it_host_step_create(it_ctx* ctx, it_dtype dtype, int32_t group_slices, int32_t seq, int32_t head_dim,
+                              int32_t causal, int32_t n_streams, it_host_step** out);
+it_status it_host_step_run(it_host_step* step, it_stream* stream, int32_t n_slices, const void* q, const void* k,
+                           const void* v, const void* d_o, void* o, float* lse, void* dq, void* dk, void* dv,
+                           int32_t copies_only);
+it_status it_host_step_destroy(it_host_step* step);
 
 /* Backward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * there every op allocates its own buffers, src/tensor.rs:63-84.)

@@ -47,6 +47,9 @@ SIGNATURES = {
     "it_flash_attention_bwd_workspace_bytes": [_c.c_int, _i32, _i32, _i32, _i32, _c.POINTER(_c.c_size_t)],
     "it_flash_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],
     "it_attention_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
+    "it_host_step_create": [_vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _c.POINTER(_vp)],
+    "it_host_step_run": [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
+    "it_host_step_destroy": [_vp],
     "it_linear_scatter_add": [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _c.POINTER(_vp), _i32, _i32],
     "it_attention_cross_fwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "it_attention_bwd": [_vp, _vp, _c.c_int, _i32, _i32, _i32, _i32, _i32] + [_vp] * 9 + [_vp, _c.c_size_t],

@@ -8,7 +8,7 @@
 // operands is the sum of the six term products of order above 2^-24:
 //     a b ~= a_hi b_hi + a_hi b_mid + a_mid b_hi + a_hi b_lo + a_mid b_mid + a_lo b_hi,
 // six tcgen05.mma into one fp32 accumulator.  Q K^T and P V are done that way; the softmax between them is
-// the same fp32 online softmax as in the bf16 kernels.  Measured against the CPU oracle: at most 6e-6 on O and 4e-6 on LSE.
+// the same fp32 online softmax as in the bf16 kernels.  Measured against the scalar fp32 restatement of the reference kernels: at most 6e-6 on O and 4e-6 on LSE.
 //
 // One CTA owns one 128-row query tile of one (batch, head) slice and walks the key tiles:
 //   warps 0-3 : softmax, one thread per query row: S from TMEM, P = 2^(s*c - m) split into three packed bf16

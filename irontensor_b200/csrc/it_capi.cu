@@ -74,6 +74,19 @@ struct it_stream {
 struct it_event {
   cudaEvent_t e = nullptr;
 };
+// Device buffers, streams and events of it_host_step_*: everything a forward + backward over host-resident tensors
+// needs, allocated once.
+struct it_host_step {
+  it_ctx* ctx = nullptr;
+  it_dtype dtype = IT_BF16;
+  int32_t group_slices = 0, S = 0, D = 0, causal = 1, n_streams = 0;
+  size_t tensor_bytes = 0, lse_bytes = 0, ws_bytes = 0;   // per group
+  static constexpr int MAX_STREAMS = 4;
+  it_stream streams[MAX_STREAMS];
+  cudaEvent_t done[MAX_STREAMS] = {};
+  cudaEvent_t start = nullptr;
+  uint8_t* dev[MAX_STREAMS] = {};   // per stream: q, k, v, dO, o, dq, dk, dv, lse, workspace
+};
 
 namespace {
 
@@ -1227,6 +1240,113 @@ it_status it_flash_attention_bwd_noalloc(it_ctx* ctx, it_stream* stream, it_dtyp
   // so nothing left in the array by an earlier call is read.
   return it_flash_attention_bwd(ctx, stream, dtype, B, H, S, D, causal, q, k, v, o, d_o, lse, dq, dk, dv, scratch,
                                 IT_NOALLOC_SCRATCH_BYTES);
+}
+
+it_status it_host_step_destroy(it_host_step* hs) {
+  if (hs == nullptr) return IT_OK;
+  if (hs->ctx != nullptr) cudaSetDevice(hs->ctx->device);
+  for (int i = 0; i < it_host_step::MAX_STREAMS; ++i) {
+    if (hs->streams[i].s != nullptr) {
+      cudaStreamSynchronize(hs->streams[i].s);
+      cudaStreamDestroy(hs->streams[i].s);
+    }
+    if (hs->done[i] != nullptr) cudaEventDestroy(hs->done[i]);
+    if (hs->dev[i] != nullptr) cudaFree(hs->dev[i]);
+  }
+  if (hs->start != nullptr) cudaEventDestroy(hs->start);
+  delete hs;
+  return IT_OK;
+}
+
+it_status it_host_step_create(it_ctx* ctx, it_dtype dtype, int32_t group_slices, int32_t S, int32_t D, int32_t causal,
+                              int32_t n_streams, it_host_step** out) {
+  if (ctx == nullptr || out == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  *out = nullptr;
+  if (dtype != IT_F32 && dtype != IT_BF16) return fail(IT_ERR_PRECISION, "dtype %d is not F32 or BF16", (int)dtype);
+  if (group_slices < 1 || group_slices > 65535 || S < 1) return fail(IT_ERR_INVALID_ARG, "bad group size or sequence length");
+  if (D < 1 || D > 128) return fail(IT_ERR_UNSUPPORTED_SHAPE, "head_dim must be in 1..128, got %d", D);
+  if (n_streams < 1 || n_streams > it_host_step::MAX_STREAMS)
+    return fail(IT_ERR_INVALID_ARG, "n_streams must be in 1..%d", it_host_step::MAX_STREAMS);
+  IT_CUDA(cudaSetDevice(ctx->device));
+  it_host_step* hs = new (std::nothrow) it_host_step;
+  if (hs == nullptr) return fail(IT_ERR_CUDA, "out of host memory");
+  hs->ctx = ctx;
+  hs->dtype = dtype;
+  hs->group_slices = group_slices;
+  hs->S = S;
+  hs->D = D;
+  hs->causal = causal != 0;
+  hs->n_streams = n_streams;
+  auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+  hs->tensor_bytes = up(static_cast<size_t>(group_slices) * S * D * (dtype == IT_F32 ? 4 : 2));
+  hs->lse_bytes = up(static_cast<size_t>(group_slices) * S * 4);
+  hs->ws_bytes = bwd_workspace_layout(dtype, group_slices, S, D).total;
+  const size_t per_stream = 8 * hs->tensor_bytes + hs->lse_bytes + hs->ws_bytes;
+  cudaError_t e = cudaEventCreateWithFlags(&hs->start, cudaEventDisableTiming);
+  for (int i = 0; i < n_streams && e == cudaSuccess; ++i) {
+    e = cudaStreamCreateWithFlags(&hs->streams[i].s, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs->done[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&hs->dev[i]), per_stream);
+  }
+  if (e != cudaSuccess) {
+    it_host_step_destroy(hs);
+    return fail(IT_ERR_CUDA, "it_host_step_create: %s", cudaGetErrorString(e));
+  }
+  *out = hs;
+  return IT_OK;
+}
+
+it_status it_host_step_run(it_host_step* hs, it_stream* stream, int32_t n_slices, const void* hq, const void* hk,
+                           const void* hv, const void* hdo, void* ho, float* hlse, void* hdq, void* hdk, void* hdv,
+                           int32_t copies_only) {
+  if (hs == nullptr || stream == nullptr) return fail(IT_ERR_INVALID_ARG, "null argument");
+  if (n_slices < 0) return fail(IT_ERR_INVALID_ARG, "negative dimension");
+  if (n_slices == 0) return IT_OK;
+  if (hq == nullptr || hk == nullptr || hv == nullptr || hdo == nullptr || ho == nullptr || hdq == nullptr || hdk == nullptr ||
+      hdv == nullptr)
+    return fail(IT_ERR_INVALID_ARG, "null tensor");
+  it_ctx* ctx = hs->ctx;
+  IT_CUDA(cudaSetDevice(ctx->device));
+  const size_t esz = hs->dtype == IT_F32 ? 4 : 2;
+  const size_t slice_bytes = static_cast<size_t>(hs->S) * hs->D * esz;
+  // the groups start after what the caller's stream has enqueued so far (the host tensors may be results of it)
+  IT_CUDA(cudaEventRecord(hs->start, stream->s));
+  int used = 0;
+  for (int32_t b0 = 0, g = 0; b0 < n_slices; b0 += hs->group_slices, ++g) {
+    const int32_t n = std::min(hs->group_slices, n_slices - b0);
+    const int si = g % hs->n_streams;
+    used = std::max(used, si + 1);
+    it_stream* st = &hs->streams[si];
+    uint8_t* base = hs->dev[si];
+    uint8_t* d[8];
+    for (int i = 0; i < 8; ++i) d[i] = base + i * hs->tensor_bytes;   // q k v dO o dq dk dv
+    float* dlse = reinterpret_cast<float*>(base + 8 * hs->tensor_bytes);
+    void* ws = base + 8 * hs->tensor_bytes + hs->lse_bytes;
+    const size_t bytes = n * slice_bytes, off = b0 * slice_bytes;
+    if (g < hs->n_streams) IT_CUDA(cudaStreamWaitEvent(st->s, hs->start, 0));
+    const void* src[4] = {hq, hk, hv, hdo};
+    for (int i = 0; i < 4; ++i)
+      IT_CUDA(cudaMemcpyAsync(d[i], static_cast<const uint8_t*>(src[i]) + off, bytes, cudaMemcpyHostToDevice, st->s));
+    if (!copies_only) {
+      it_status rc = it_flash_attention_fwd(ctx, st, hs->dtype, 1, n, hs->S, hs->D, hs->causal, d[0], d[1], d[2], d[4], dlse);
+      if (rc != IT_OK) return rc;
+      rc = it_flash_attention_bwd(ctx, st, hs->dtype, 1, n, hs->S, hs->D, hs->causal, d[0], d[1], d[2], d[4], d[3], dlse, d[5],
+                                  d[6], d[7], ws, hs->ws_bytes);
+      if (rc != IT_OK) return rc;
+    }
+    void* dst[4] = {ho, hdq, hdk, hdv};
+    const int from[4] = {4, 5, 6, 7};
+    for (int i = 0; i < 4; ++i)
+      IT_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(dst[i]) + off, d[from[i]], bytes, cudaMemcpyDeviceToHost, st->s));
+    if (hlse != nullptr)
+      IT_CUDA(cudaMemcpyAsync(hlse + static_cast<size_t>(b0) * hs->S, dlse, static_cast<size_t>(n) * hs->S * 4,
+                              cudaMemcpyDeviceToHost, st->s));
+  }
+  for (int i = 0; i < used; ++i) {   // the caller's stream continues when every group has been downloaded
+    IT_CUDA(cudaEventRecord(hs->done[i], hs->streams[i].s));
+    IT_CUDA(cudaStreamWaitEvent(stream->s, hs->done[i], 0));
+  }
+  return IT_OK;
 }
 
 it_status it_attention_status_poll(it_ctx* ctx, it_stream* stream, int32_t* device_status) {

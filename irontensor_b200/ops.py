@@ -686,50 +686,40 @@ def attention_backward_recompute(grad_output, q, k, v, o=None, lse=None, causal=
 
 
 class HostAttentionStep:
-    """Forward + backward for tensors that live in page-locked HOST memory.
+    """Forward + backward for tensors that live in page-locked HOST memory (it_host_step_* of the C ABI).
 
-    The reference's tensors are unified memory, so its ops never copy; on a discrete GPU a caller with
-    host data pays PCIe both ways.  This helper hides most of it: the (batch*head) slices are cut into
-    `chunks` groups, and each group runs upload -> flash_attention -> attention_backward_recompute ->
-    download on its own stream (three streams in rotation), so one group's upload, another's kernels
-    and a third's download proceed at the same time on the two copy engines and the SMs.
-    Device buffers are allocated once, in the constructor."""
+    The reference's tensors are unified memory, so its ops never copy; on a discrete GPU a caller with host data
+    pays the host link both ways.  The library hides most of it: the (batch*head) slices are cut into `chunks`
+    groups, and each group runs upload -> forward -> backward -> download on one of `n_streams` streams in rotation,
+    so one group's upload, another's kernels and a third's download proceed at the same time on the two copy
+    engines and the SMs.  The loop over the groups runs inside the library (one call per step), so groups can be
+    small.  Device buffers, streams and events are allocated once, in the constructor."""
 
     def __init__(self, n_slices, S, D, precision=Precision.BF16, causal=True, chunks=4, n_streams=3):
-        torch = _torch()
-        self.S, self.D, self.precision, self.causal = S, D, precision, causal
+        self.ctx = context()
+        self.n_slices, self.S, self.D, self.precision = n_slices, S, D, precision
         chunks = max(1, min(chunks, n_slices))
-        per = -(-n_slices // chunks)
-        self.ranges = [(b, min(n_slices, b + per)) for b in range(0, n_slices, per)]
-        self.streams = [torch.cuda.Stream() for _ in range(min(n_streams, len(self.ranges)))]
-        self.dev = [[Tensor.empty([1, per, S, D], precision) for _ in range(4)] for _ in self.streams]
-        self.done = [torch.cuda.Event() for _ in self.streams]
+        self.group = -(-n_slices // chunks)
+        h = ctypes.c_void_p()
+        _lib.check(self.ctx.lib.it_host_step_create(self.ctx.handle, _dtype_code(precision), self.group, S, D, int(causal),
+                                                    max(1, min(n_streams, chunks, 4)), ctypes.byref(h)))
+        self.handle = h
 
-    def run(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv, copies_only=False):
-        """All arguments: pinned torch tensors [n_slices, S, D].  Enqueues the whole step; the calling
-        stream continues only after every group's download has finished.  Nothing is waited for here: drain the
-        stream and check the device status (CommandBatch.sync(), context().poll_status()) before reading the
-        host tensors.  copies_only=True enqueues the same uploads and downloads on the same streams without the
-        kernels (what the host link alone costs; the downloaded bytes are then whatever the buffers held)."""
-        torch = _torch()
-        cur = torch.cuda.current_stream()
-        start = torch.cuda.Event()
-        start.record(cur)
-        for i, (b0, b1) in enumerate(self.ranges):
-            st = self.streams[i % len(self.streams)]
-            bufs = self.dev[i % len(self.streams)]
-            n = b1 - b0
-            shape = [1, n, self.S, self.D]
-            with torch.cuda.stream(st):
-                st.wait_event(start)
-                tq, tk, tv, tdo = (Tensor(t._data[: n * self.S * self.D], shape, self.precision) for t in bufs)
-                tq.upload_from(hq[b0:b1]), tk.upload_from(hk[b0:b1]), tv.upload_from(hv[b0:b1]), tdo.upload_from(hdo[b0:b1])
-                if copies_only:
-                    out, gq, gk, gv = tq, tk, tv, tdo
-                else:
-                    out = flash_attention(tq, tk, tv, self.causal)
-                    gq, gk, gv = attention_backward_recompute(tdo, tq, tk, tv, o=out, lse=out.lse, causal=self.causal)
-                out.download_to(ho[b0:b1]), gq.download_to(hdq[b0:b1]), gk.download_to(hdk[b0:b1]), gv.download_to(hdv[b0:b1])
-                self.done[i % len(self.streams)].record(st)
-        for ev in self.done:
-            cur.wait_event(ev)
+    def run(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv, hlse=None, copies_only=False):
+        """All arguments: pinned torch tensors [n_slices, S, D] (hlse [n_slices, S], optional).  Enqueues the whole step;
+        torch's current stream continues only after every group's download has finished.  Nothing is waited for
+        here: drain the stream and check the device status (CommandBatch.sync(), context().poll_status()) before
+        reading the host tensors.  copies_only=True enqueues the same uploads and downloads on the same streams
+        without the kernels (what the host link alone costs)."""
+        for t in (hq, hk, hv, hdo, ho, hdq, hdk, hdv):
+            assert t.is_pinned() and t.numel() == self.n_slices * self.S * self.D
+        _lib.check(self.ctx.lib.it_host_step_run(self.handle, self.ctx.stream(), self.n_slices, hq.data_ptr(), hk.data_ptr(),
+                                                 hv.data_ptr(), hdo.data_ptr(), ho.data_ptr(),
+                                                 None if hlse is None else hlse.data_ptr(), hdq.data_ptr(), hdk.data_ptr(),
+                                                 hdv.data_ptr(), int(copies_only)))
+
+    def __del__(self):
+        try:
+            self.ctx.lib.it_host_step_destroy(self.handle)
+        except Exception:
+            pass
