@@ -13,9 +13,10 @@ is used only for the barrier and the max-over-ranks of the device times.
 Prints ONE JSON line:
   value        whole-job TFLOP/s with inputs resident in HBM (FLOPs: fwd 2*B*H*S^2*D, bwd 5*B*H*S^2*D,
                the causal-halved FlashAttention convention), device time from CUDA events, max over ranks
-  e2e          the same metric through the package's public ops with HOST tensors (HostAttentionStep):
+  e2e          the same metric through the library's host-tensor call (it_host_step_run via ops.HostAttentionStep):
                every step uploads Q,K,V,dO from pinned memory and downloads O,dQ,dK,dV inside the timed
-               region, slices in 16 groups on rotating streams so copies and kernels overlap
+               region, slices in 16 groups on rotating streams so copies and kernels overlap; copy_only_ms
+               (the same copies without the kernels) and host_issue_ms beside it
   roofline     the backward main kernel (dominant) against the measured dense-bf16 peak
   cpu_baseline the CPU oracle timed on this box's host cores on a bounded sample (rank 0, N=1 only)
 --impl reference times the reference's algorithm on the host cores instead (the CPU oracle: the
