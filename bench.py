@@ -329,17 +329,18 @@ def run_ours(args, rank, world, local_rank):
         step_device()
         ev[i][1].record()
         if nbh:
-            fwd_ms.append(ctx.kernel_ms(0))   # waits for this step's kernels
-            bwd_ms.append(ctx.kernel_ms(1))
+            bwd_ms.append(ctx.kernel_ms(1))   # waits for this step's kernels
     barrier()
     launches = ctx.launch_count() - launches0
     ctx.poll_status()
-    if nbh and use_timers2:   # the small passes of the backward, timed in three extra steps outside the timed region
-        ctx.enable_kernel_timing(2)
+    if nbh:   # the forward kernel and the small passes of the backward, timed in three extra steps outside the timed region
+        ctx.enable_kernel_timing(3 if use_timers2 else 2)
         for _ in range(3):
             step_device()
-            prep_ms.append(ctx.kernel_ms(2))
-            fin_ms.append(ctx.kernel_ms(3))
+            fwd_ms.append(ctx.kernel_ms(0))
+            if use_timers2:
+                prep_ms.append(ctx.kernel_ms(2))
+                fin_ms.append(ctx.kernel_ms(3))
         ctx.enable_kernel_timing(1)
     step_ms = [a.elapsed_time(b) for a, b in ev]
     my_ms = sum(step_ms) / steps

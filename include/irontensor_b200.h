@@ -322,10 +322,10 @@ it_status it_ctx_launch_count(it_ctx* ctx, uint64_t* out);
 
 /* Device-side timers around the two main kernels, the counterpart of the reference's
  * OpCategory::FlashAttention timer (src/ops/flash_attention.rs:77, src/profile/timer.rs:27-36),
- * which measures host encode time.  While enabled (1), each it_flash_attention_fwd / _bwd call
- * records a CUDA event before and after its main kernel on the call's stream; with enable = 2 the backward's
- * prepare and finish passes are bracketed too (four more event records per call: microseconds, visible on
- * the smallest shapes).
+ * which measures host encode time.  enable = 1: each it_flash_attention_bwd call records a CUDA event before
+ * and after its main kernel on the call's stream; 2: the forward kernel of it_flash_attention_fwd as well; 3: the
+ * backward's prepare and finish passes too.  Every bracket is two event records in the stream: a few
+ * microseconds each, visible on the smallest shapes (12 us of a 50 us step), which is why the levels exist.
  * it_ctx_kernel_ms waits for the most recent such pair and returns the time between them
  * (which = 0: forward kernel, 1: backward main kernel, 2: backward prepare pass, 3: backward finish pass; 2 and 3
  * exist for the tensor-core backward only).  it_ctx_kernel_tag gives the reference's profiler tag for what a timer

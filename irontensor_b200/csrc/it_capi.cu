@@ -60,7 +60,7 @@ struct it_ctx {
   cudaStream_t status_stream = nullptr;   // reads the status word without touching a caller's stream
   std::mutex status_mutex;      // h_status and status_stream are shared by every thread using the context
   EncodeTiledFn encode = nullptr;
-  int timing = 0;               // 1: events around the two main kernels; 2: around the backward's prepare and finish passes too
+  int timing = 0;               // events around: 1 the backward main kernel; 2 the forward kernel too; 3 the backward's prepare and finish passes too
   // [forward | backward main | backward prepare | backward finish][start | stop]; the prepare pass starts where the
   // previous timer stopped only in time, not in events: three pairs share the boundaries prepare|main|finish
   cudaEvent_t ev[4][2] = {};
@@ -316,9 +316,9 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.dec_part_o = nullptr;
   p.dec_part_ml = nullptr;
   const int n_ctas_per_slice = (S + T::BM * T::QT_PER_CTA - 1) / (T::BM * T::QT_PER_CTA);
-  if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
+  if (ctx->timing >= 2) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
   kernel<<<static_cast<unsigned>(n_ctas_per_slice) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
-  if (ctx->timing) {
+  if (ctx->timing >= 2) {
     IT_CUDA(cudaEventRecord(ctx->ev[0][1], s));
     ctx->ev_valid[0] = true;
   }
@@ -389,7 +389,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   float* delta = reinterpret_cast<float*>(ws + w.delta_off);
   const size_t n_dq = static_cast<size_t>(BH) * S * D;
   const long long rows_pad = static_cast<long long>(BH) * w.S_pad;
-  if (ctx->timing >= 2) IT_CUDA(cudaEventRecord(ctx->ev[2][0], s));
+  if (ctx->timing >= 3) IT_CUDA(cudaEventRecord(ctx->ev[2][0], s));
   it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad / 8 + 7) / 8), 256, 0, s>>>(   // 8 rows per warp, 8 warps
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, dq_accum, S,
       w.S_pad, BH, stv);
@@ -416,7 +416,7 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   const char* force = getenv("IT_BWD_KEY_TILES");
   const bool two_tiles = (D == 64) && n_kt >= 2 &&
                          (force != nullptr ? force[0] == '2' : static_cast<long long>(n_kt) * B * Hkv > 2LL * ctx->sm_count);
-  if (ctx->timing >= 2) {
+  if (ctx->timing >= 3) {
     IT_CUDA(cudaEventRecord(ctx->ev[2][1], s));
     ctx->ev_valid[2] = true;
   }
@@ -432,11 +432,11 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
   }
-  if (ctx->timing >= 2) IT_CUDA(cudaEventRecord(ctx->ev[3][0], s));
+  if (ctx->timing >= 3) IT_CUDA(cudaEventRecord(ctx->ev[3][0], s));
   const size_t n4 = n_dq / 4;
   it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
       dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, sq, rf);
-  if (ctx->timing >= 2) {
+  if (ctx->timing >= 3) {
     IT_CUDA(cudaEventRecord(ctx->ev[3][1], s));
     ctx->ev_valid[3] = true;
   }
@@ -1381,7 +1381,7 @@ it_status it_ctx_enable_kernel_timing(it_ctx* ctx, int32_t enable) {
     for (int a = 0; a < 4; ++a)
       for (int b = 0; b < 2; ++b) IT_CUDA(cudaEventCreate(&ctx->ev[a][b]));
   }
-  ctx->timing = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
+  ctx->timing = enable < 0 ? 0 : (enable > 3 ? 3 : enable);
   return IT_OK;
 }
 

@@ -69,7 +69,8 @@ class _Context:
         return n.value
 
     def enable_kernel_timing(self, on=True):
-        """False / 0: off; True / 1: the two main kernels; 2: the backward's prepare and finish passes as well."""
+        """False / 0: off; True / 1: the backward main kernel; 2: the forward kernel too; 3: the backward's prepare and
+        finish passes as well."""
         _lib.check(self.lib.it_ctx_enable_kernel_timing(self.handle, int(on)))
 
     def kernel_tag(self, which):

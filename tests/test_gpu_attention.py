@@ -466,6 +466,40 @@ def test_host_step_overlapped_chunks_match_device_resident(it_ctx):
     assert np.array_equal(got[0], whole[0][0])
     assert np.abs(got[1] - whole[2][0]).max() <= 2e-2     # dQ: reduction order may differ
     assert np.array_equal(got[2], whole[3][0]) and np.array_equal(got[3], whole[4][0])
+    # fp32 tensors (the reference's own precision), an uneven last group, and the log-sum-exp downloaded as well
+    BH, S, D = 5, 70, 32
+    q, k, v, d_o = seeded(78, 1, BH, S, D)
+    whole = gu.run_fwd_bwd(it_ctx, q, k, v, d_o, True, False)
+    host_in = [torch.from_numpy(np.ascontiguousarray(x[0])).pin_memory() for x in (q, k, v, d_o)]
+    host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(4)]
+    host_lse = torch.empty((BH, S), dtype=torch.float32).pin_memory()
+    step = HostAttentionStep(BH, S, D, Precision.FP32, causal=True, chunks=3)      # groups of 2, 2, 1
+    step.run(*host_in, *host_out, hlse=host_lse)
+    torch.cuda.synchronize()
+    assert it_ctx.poll_status() == 0
+    for got_t, want in zip(host_out, (whole[0][0], whole[2][0], whole[3][0], whole[4][0])):
+        assert np.array_equal(got_t.numpy(), want)
+    assert np.array_equal(host_lse.numpy(), whole[1][0])
+    # the copies alone leave the status clean and touch nothing but the host tensors
+    step.run(*host_in, *host_out, copies_only=True)
+    torch.cuda.synchronize()
+    assert it_ctx.poll_status() == 0
+
+
+def test_kernel_timers_and_profiler_tags(it_ctx):
+    """The device-side timers that stand in for the reference's profiler categories (OpCategory::FlashAttention,
+    src/ops/flash_attention.rs:77; attn_bwd/* in src/train/helpers.rs:126-183): levels 1 to 3 bracket more kernels."""
+    assert it_ctx.kernel_tag(0) == "FlashAttention"
+    assert it_ctx.kernel_tag(1).startswith("attn_bwd/") and "grad_qk" in it_ctx.kernel_tag(1)
+    assert it_ctx.kernel_tag(2) == "attn_bwd/prepare" and it_ctx.kernel_tag(3) == "attn_bwd/finish"
+    q, k, v, d_o = seeded(5, 1, 2, 256, 64, bf16=True)
+    it_ctx.enable_kernel_timing(3)
+    try:
+        gu.run_fwd_bwd(it_ctx, q, k, v, d_o, True, True)
+        times = [it_ctx.kernel_ms(w) for w in range(4)]
+        assert all(0.0 < t < 50.0 for t in times), times
+    finally:
+        it_ctx.enable_kernel_timing(0)
 
 
 @pytest.mark.parametrize("shape,bf16", [((2, 3, 256, 64), True), ((1, 2, 300, 128), True), ((2, 4, 32, 16), False),
