@@ -38,7 +38,7 @@ struct FwdTraits {
   static constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;
   static constexpr int SMEM_V = SMEM_K + STAGES * TILE_BYTES;
   static constexpr int SMEM_BAR = SMEM_V + STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 2 + 4 * STAGES + 6;
+  static constexpr int NUM_BARS = 4 + 4 * STAGES + 6 + 4;
   static constexpr int SMEM_MISC = SMEM_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = SMEM_MISC + 16;
   static constexpr int THREADS = 384;
@@ -55,6 +55,8 @@ struct FwdParams {
   int causal;
   float scale_log2;     // 1/sqrt(D) * log2(e)
   int kv_group;         // query heads per K/V head (grouped-query attention; 1 otherwise)
+  int group_slices;     // fa_fwd_sm100_kernel: slices per group of its work-item order (their K and V fit in L2)
+  int* work_counter;    // fa_fwd_sm100_kernel: zeroed before the launch when the grid is smaller than the number of work items, else null
   // decode instantiation of the long-sequence kernel only (one new token against a key/value cache):
   int dec_tiles_per_split;   // key tiles per CTA
   int dec_n_splits;
@@ -72,34 +74,64 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::SMEM_BAR);
   uint64_t* q_full = bars;                        // [2]
-  uint64_t* k_full = q_full + 2;                  // [STAGES]
+  uint64_t* q_empty = q_full + 2;                 // [2] every S MMA of the work item that reads Q_t has completed
+  uint64_t* k_full = q_empty + 2;                 // [STAGES]
   uint64_t* k_empty = k_full + T::STAGES;
   uint64_t* v_full = k_empty + T::STAGES;
   uint64_t* v_empty = v_full + T::STAGES;
   uint64_t* s_full = v_empty + T::STAGES;         // [2]
   uint64_t* p_full = s_full + 2;                  // [2]
   uint64_t* o_done = p_full + 2;                  // [2]
+  uint64_t* sched_full = o_done + 2;              // [2] item index written (1 arrival)
+  uint64_t* sched_empty = sched_full + 2;         // [2] every role is through with the item (producer, MMA thread, 8 softmax warps)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + T::SMEM_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::SMEM_MISC + 4);
+  volatile int* sched_item = reinterpret_cast<volatile int*>(smem + T::SMEM_MISC + 8);   // [2] item index, -1: no more
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int S = prm.S;
   const int n_kv_total = (S + T::BN - 1) / T::BN;
   const int n_pairs = (S + 2 * T::BM - 1) / (2 * T::BM);
-  // Head-major order: the CTAs resident at one time belong to a few (batch, head) slices, so the K/V
-  // tiles they all stream stay in L2.  Within a slice the last query tiles (most keys) go first.
-  const int bh = static_cast<int>(blockIdx.x) / n_pairs;
-  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) % n_pairs;
-  const int hd = bh % prm.st.heads, bt = bh / prm.st.heads;   // TMA coordinates of the slice
-  const int hkv = hd / prm.kv_group;                          // the K/V head this query head reads
-  int n_kv[2];
+  // Work items are (slice, pair of query tiles).  The grid is at most one CTA per SM and a CTA walks items in a loop
+  // in which every role runs ahead on its own: the producer fetches the next item's Q and first K/V tiles while the
+  // current item's last tiles are in the softmax, and the MMA thread issues the next item's first S tiles right
+  // behind the current item's last P V, so that a CTA pays set-up, first-load latency and tear-down once and not
+  // once per item (at a thousand keys an item is a handful of tiles long and they were a quarter of its life).
+  // Item order: slices in groups whose K and V fit in L2 together; within a group the pairs with the most key
+  // tiles first, all slices of the group for one pair, then the next pair.  A CTA's first item is its own index;
+  // the following ones it draws from a counter in global memory (warp 3), one item ahead of the softmax groups, and
+  // hands to the other roles through a two-slot ring in shared memory: the lightest items come last, so the CTAs
+  // finish within about one small item of each other whatever the mix.
+  const int n_items = prm.BH * n_pairs;
+  const int G = static_cast<int>(gridDim.x);
+  struct Item {
+    int bh, pair, hd, bt, hkv, n_kv[2], n_iter;
+  };
+  auto decode = [&](int idx, Item& it) {
+    const int per_group = n_pairs * prm.group_slices;
+    const int g = idx / per_group, r = idx - g * per_group;
+    const int gs = min(prm.group_slices, prm.BH - g * prm.group_slices);
+    it.pair = n_pairs - 1 - r / gs;
+    it.bh = g * prm.group_slices + r % gs;
+    it.hd = it.bh % prm.st.heads;   // TMA coordinates of the slice
+    it.bt = it.bh / prm.st.heads;
+    it.hkv = it.hd / prm.kv_group;  // the K/V head this query head reads
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int qt = 2 * pair + t;
-    n_kv[t] = (qt * T::BM < S) ? (prm.causal ? min(qt + 1, n_kv_total) : n_kv_total) : 0;
-  }
-  const int n_iter = max(n_kv[0], n_kv[1]);
+    for (int t = 0; t < 2; ++t) {
+      const int qt = 2 * it.pair + t;
+      it.n_kv[t] = (qt * T::BM < S) ? (prm.causal ? min(qt + 1, n_kv_total) : n_kv_total) : 0;
+    }
+    it.n_iter = max(it.n_kv[0], it.n_kv[1]);
+  };
+  // The n-th item of this CTA, as the roles other than the scheduler see it: 1 = there is one, 0 = no more, -1 = gave up.
+  auto fetch = [&](uint32_t n, Item& it) -> int {
+    if (!mbar_wait(&sched_full[n & 1], (n >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return -1;
+    const int idx = sched_item[n & 1];
+    if (idx < 0) return 0;
+    decode(idx, it);
+    return 1;
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -112,9 +144,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (*reinterpret_cast<volatile int*>(prm.status) != 0) *abort_flag = 1;
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
       mbar_init(&o_done[i], 1);
+      mbar_init(&sched_full[i], 1);
+      mbar_init(&sched_empty[i], 10);
     }
     for (int i = 0; i < T::STAGES; ++i) {
       mbar_init(&k_full[i], 1);
@@ -125,35 +160,40 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     fence_mbar_init();
     fence_proxy_async_smem();
   }
-  // Key/value tile j into its ring stage (producer thread only).
-  auto load_kv = [&](int j) -> bool {
-    const int st = j % T::STAGES;
-    const uint32_t ph = (j / T::STAGES) & 1;
+  // Key/value tile j of an item into ring slot g (g counts the tiles of all items of this CTA; producer thread only).
+  auto load_kv = [&](uint32_t g, int j, const Item& it) -> bool {
+    const int st = static_cast<int>(g % T::STAGES);
+    const uint32_t ph = (g / T::STAGES) & 1;
     if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return false;
     mbar_arrive_expect_tx(&k_full[st], T::TILE_BYTES);
     for (int b = 0; b < T::NBLK; ++b)
-      tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64, j * T::BN, hkv, bt);
+      tma_load_4d(smem + T::SMEM_K + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_k, &k_full[st], b * 64, j * T::BN, it.hkv,
+                  it.bt);
     if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return false;
     mbar_arrive_expect_tx(&v_full[st], T::TILE_BYTES);
     for (int b = 0; b < T::NBLK; ++b)
-      tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64, j * T::BN, hkv, bt);
+      tma_load_4d(smem + T::SMEM_V + st * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_v, &v_full[st], b * 64, j * T::BN, it.hkv,
+                  it.bt);
     return true;
   };
-  // The query tiles and the first key/value tile go out before the CTA-wide set-up (tensor-memory allocation,
-  // barrier, register hand-over), so their round trip to memory runs under it: at a thousand keys a CTA lives for a
-  // handful of tiles and that wait is a visible part of its life.  Nothing is loaded into a CTA that will not run.
+  auto load_q = [&](int t, const Item& it) {
+    mbar_arrive_expect_tx(&q_full[t], T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
+                  (2 * it.pair + t) * T::BM, it.hd, it.bt);
+  };
+  // The first item's query tiles and first key/value tile go out before the CTA-wide set-up (tensor-memory allocation,
+  // barrier, register hand-over), so their round trip to memory runs under it.  Nothing is loaded into a CTA that
+  // will not run.
   if (threadIdx.x == 0 && *abort_flag == 0) {
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
-    for (int t = 0; t < 2; ++t) {
-      if (n_kv[t] == 0) continue;
-      mbar_arrive_expect_tx(&q_full[t], T::TILE_BYTES);
-      for (int b = 0; b < T::NBLK; ++b)
-        tma_load_4d(smem + T::SMEM_Q + t * T::TILE_BYTES + b * T::BLOCK_BYTES, &tmap_q, &q_full[t], b * 64,
-                    (2 * pair + t) * T::BM, hd, bt);
-    }
-    if (n_iter > 0) load_kv(0);
+    Item it;
+    decode(static_cast<int>(blockIdx.x), it);
+    for (int t = 0; t < 2; ++t)
+      if (it.n_kv[t] > 0) load_q(t, it);
+    if (it.n_iter > 0) load_kv(0, 0, it);
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, T::TMEM_COLS);
@@ -173,10 +213,26 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // nothing to do
     } else if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
-      // (the query tiles and key/value tile 0 were issued by this thread before the set-up barrier)
+      // (the first item's query tiles and key/value tile 0 were issued by this thread before the set-up barrier)
       if (lane == 0) {
-        for (int j = 1; j < n_iter; ++j)
-          if (!load_kv(j)) break;
+        uint32_t g = 0;               // key/value tiles issued so far
+        uint32_t q_uses[2] = {0, 0};  // items so far that had query tile t
+        bool ok = true;
+        Item it;
+        for (uint32_t k = 0; ok && fetch(k, it) == 1; ++k) {
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (it.n_kv[t] == 0) continue;
+            if (k > 0) {
+              // the buffer's previous tile has been read by its last S MMA
+              ok = mbar_wait(&q_empty[t], (q_uses[t] - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY);
+              if (ok) load_q(t, it);
+            }
+            ++q_uses[t];
+          }
+          for (int j = 0; j < it.n_iter && ok; ++j, ++g)
+            if (k > 0 || j > 0) ok = load_kv(g, j, it);
+          mbar_arrive(&sched_empty[k & 1]);
+        }
       }
     } else if (warp == 1) {
       // ------------------------------------------------------------ MMA issuer (one thread)
@@ -204,38 +260,80 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     (!first || kk > 0) ? 1u : 0u);
         };
         bool ok = true;
-        // prologue: S_t(0)
-        ok = mbar_wait(&k_full[0], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (n_kv[t] == 0) continue;
-          ok = mbar_wait(&q_full[t], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(t, 0);
-        }
-        if (ok) umma_commit(&k_empty[0]);
-        for (int j = 0; j < n_iter && ok; ++j) {
-          const int st = j % T::STAGES;
-          const uint32_t ph = (j / T::STAGES) & 1;
-          const int st_n = (j + 1) % T::STAGES;
-          const uint32_t ph_n = ((j + 1) / T::STAGES) & 1;
-          const bool have_next = (j + 1 < n_iter);
-          if (have_next) ok = mbar_wait(&k_full[st_n], ph_n, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-          if (!ok) break;
-          ok = mbar_wait(&v_full[st], ph, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
-          if (!ok) break;
+        uint32_t g0 = 0;               // ring slot counter of the current item's key tile 0
+        uint32_t q_uses[2] = {0, 0};   // items before the current one that had query tile t
+        uint32_t pv_cnt[2] = {0, 0};   // P tiles consumed so far
+        // S_t(0) of an item: issued behind the previous item's last P V (the tensor core runs its MMAs in issue
+        // order, so S_t may overwrite the P_t that P V still reads), ahead of that item's epilogue.
+        auto first_s = [&](const Item& it, uint32_t g) -> bool {
+          const int st = static_cast<int>(g % T::STAGES);
+          if (!mbar_wait(&k_full[st], (g / T::STAGES) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD)) return false;
           for (int t = 0; t < 2; ++t) {
-            if (j >= n_kv[t]) continue;
-            ok = mbar_wait(&p_full[t], j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
-            if (!ok) break;
+            if (it.n_kv[t] == 0) continue;
+            if (!mbar_wait(&q_full[t], q_uses[t] & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD)) return false;
             tc_fence_after();
-            issue_pv(t, st, j == 0);
-            if (j == n_kv[t] - 1) umma_commit(&o_done[t]);
-            if (j + 1 < n_kv[t]) issue_s(t, st_n);
+            issue_s(t, st);
+            if (it.n_kv[t] == 1) umma_commit(&q_empty[t]);
+          }
+          umma_commit(&k_empty[st]);
+          return true;
+        };
+        Item it;
+        bool have = fetch(0, it) == 1;
+        if (have) ok = first_s(it, g0);
+        for (uint32_t k = 0; have && ok; ++k) {
+          for (int j = 0; j < it.n_iter && ok; ++j) {
+            const uint32_t g = g0 + j;
+            const int st = static_cast<int>(g % T::STAGES);
+            const uint32_t ph = (g / T::STAGES) & 1;
+            const int st_n = static_cast<int>((g + 1) % T::STAGES);
+            const uint32_t ph_n = ((g + 1) / T::STAGES) & 1;
+            const bool have_next = (j + 1 < it.n_iter);
+            if (have_next) ok = mbar_wait(&k_full[st_n], ph_n, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+            if (!ok) break;
+            ok = mbar_wait(&v_full[st], ph, abort_flag, prm.status, DEV_ERR_TIMEOUT_LOAD);
+            if (!ok) break;
+            for (int t = 0; t < 2; ++t) {
+              if (j >= it.n_kv[t]) continue;
+              ok = mbar_wait(&p_full[t], pv_cnt[t] & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_SOFTMAX);
+              if (!ok) break;
+              ++pv_cnt[t];
+              tc_fence_after();
+              issue_pv(t, st, j == 0);
+              if (j == it.n_kv[t] - 1) umma_commit(&o_done[t]);
+              if (j + 1 < it.n_kv[t]) {
+                issue_s(t, st_n);
+                if (j + 2 == it.n_kv[t]) umma_commit(&q_empty[t]);   // that was the item's last read of Q_t
+              }
+            }
+            if (!ok) break;
+            umma_commit(&v_empty[st]);
+            if (have_next) umma_commit(&k_empty[st_n]);
           }
           if (!ok) break;
-          umma_commit(&v_empty[st]);
-          if (have_next) umma_commit(&k_empty[st_n]);
+          g0 += it.n_iter;
+          for (int t = 0; t < 2; ++t) q_uses[t] += (it.n_kv[t] > 0) ? 1u : 0u;
+          mbar_arrive(&sched_empty[k & 1]);
+          have = fetch(k + 1, it) == 1;
+          if (have) ok = first_s(it, g0);
+        }
+      }
+    } else if (warp == 3) {
+      // ------------------------------------------------------------ work-item scheduler (one thread)
+      if (lane == 0) {
+        for (uint32_t n = 0;; ++n) {
+          // the slot's previous item (n - 2) has been released by every role
+          if (n >= 2 && !mbar_wait(&sched_empty[n & 1], ((n >> 1) - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
+          int idx = -1;
+          if (n == 0) {
+            idx = static_cast<int>(blockIdx.x);
+          } else if (prm.work_counter != nullptr) {
+            idx = G + atomicAdd(prm.work_counter, 1);
+            if (idx >= n_items) idx = -1;
+          }
+          sched_item[n & 1] = idx;
+          mbar_arrive(&sched_full[n & 1]);
+          if (idx < 0) break;
         }
       }
     }
@@ -243,23 +341,34 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     setmaxnreg_inc<208>();
     // ------------------------------------------------------------ softmax + epilogue
     const int t = (warp - 4) >> 2;
-    const int nkv = n_kv[t];
-    if (!bad_start && nkv > 0) {
-      const int qt = 2 * pair + t;
-      const int lane_base = (warp & 3) * 32;
+    const int lane_base = (warp & 3) * 32;
+    const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + t * 128;
+    const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + 256 + t * D;
+    const float sl2 = prm.scale_log2;
+    uint32_t s_seen = 0;   // S tiles of this group consumed so far
+    uint32_t items = 0;    // items so far that had this group's query tile
+    bool ok = !bad_start;
+    Item it;
+    for (uint32_t k = 0; ok; ++k) {
+      const int got = fetch(k, it);
+      if (__any_sync(0xffffffffu, got != 1)) break;
+      const int nkv = it.n_kv[t];
+      if (nkv == 0) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sched_empty[k & 1]);
+        continue;
+      }
+      const int qt = 2 * it.pair + t;
       const int q_row = qt * T::BM + lane_base + lane;
-      const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + t * 128;
-      const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + 256 + t * D;
-      const float sl2 = prm.scale_log2;
       const int k_limit = prm.causal ? min(S - 1, q_row) : (S - 1);   // last visible key index
       float m_used = -INFINITY;
       float l_sum = 0.f;
-      bool ok = true;
       uint32_t r[128];   // this thread's row of S
       for (int j = 0; j < nkv; ++j) {
-        ok = mbar_wait(&s_full[t], j & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = mbar_wait(&s_full[t], s_seen & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        ++s_seen;
         tc_fence_after();
         // the whole row in one go: four loads in flight, one wait
 #pragma unroll
@@ -331,30 +440,34 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         mbar_arrive(&p_full[t]);
       }
       if (ok) {
-        ok = mbar_wait(&o_done[t], 0, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
+        ok = mbar_wait(&o_done[t], items & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) {
-        tc_fence_after();
-        const float inv_l = 1.0f / l_sum;
-        __nv_bfloat16* orow = prm.o + prm.st.slice(bh) + static_cast<long long>(q_row) * prm.st.row;
+      if (!ok) break;
+      ++items;
+      // The next item's first P V overwrites O_t; it is issued after this group's next arrival on p_full, which
+      // comes after these loads in program order.
+      tc_fence_after();
+      const float inv_l = 1.0f / l_sum;
+      __nv_bfloat16* orow = prm.o + prm.st.slice(it.bh) + static_cast<long long>(q_row) * prm.st.row;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld_x32(t_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-        tmem_wait_ld();
-        if (q_row < S) {
+      for (int c = 0; c < D / 32; ++c) tmem_ld_x32(t_o + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_wait_ld();
+      if (q_row < S) {
 #pragma unroll
-          for (int v = 0; v < D / 8; ++v) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
-            w.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
-            w.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
-            w.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + v * 8) = w;
-          }
-          if (prm.lse != nullptr)
-            prm.lse[static_cast<size_t>(bh) * S + q_row] = (m_used + lg2(l_sum)) * 0.6931471805599453f;
+        for (int v = 0; v < D / 8; ++v) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
+          w.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
+          w.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
+          w.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(orow + v * 8) = w;
         }
+        if (prm.lse != nullptr)
+          prm.lse[static_cast<size_t>(it.bh) * S + q_row] = (m_used + lg2(l_sum)) * 0.6931471805599453f;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sched_empty[k & 1]);
     }
   }
 

@@ -18,6 +18,7 @@
 
 #include "fa_bwd_sm100.cuh"
 #include <algorithm>
+#include <vector>
 #include <type_traits>
 
 #include "fa_fwd_sm100.cuh"
@@ -66,11 +67,40 @@ struct it_ctx {
   cudaEvent_t ev[4][2] = {};
   bool ev_valid[4] = {false, false, false, false};
   std::atomic<uint64_t> launches{0};
+  // Work-item counters of the forward kernel that walks its items in a loop: one int per live stream object (launches
+  // on one stream run one after the other, so a stream needs one counter), handed out from a pool allocated with the
+  // context so that wrapping a stream calls nothing a stream capture forbids.
+  static constexpr int WORK_SLOTS = 4096;
+  int* d_work_pool = nullptr;
+  std::mutex work_mutex;
+  std::vector<int> work_free;
+  int work_next = 0;
 };
 struct it_stream {
   cudaStream_t s = nullptr;
   bool owned = false;
+  int* d_work = nullptr;     // this stream's work-item counter; null when the pool ran out (the launcher then starts one CTA per item)
+  bool work_used = false;    // a launch has drawn from the counter
 };
+namespace {
+int* take_work_slot(it_ctx* ctx) {
+  std::lock_guard<std::mutex> lock(ctx->work_mutex);
+  if (ctx->d_work_pool == nullptr) return nullptr;
+  if (!ctx->work_free.empty()) {
+    const int i = ctx->work_free.back();
+    ctx->work_free.pop_back();
+    return ctx->d_work_pool + i;
+  }
+  return ctx->work_next < it_ctx::WORK_SLOTS ? ctx->d_work_pool + ctx->work_next++ : nullptr;
+}
+void give_work_slot(it_ctx* ctx, it_stream* stream) {
+  if (ctx == nullptr || stream->d_work == nullptr) return;
+  if (stream->work_used) cudaStreamSynchronize(stream->s);   // a kernel in flight may still draw from the counter
+  std::lock_guard<std::mutex> lock(ctx->work_mutex);
+  ctx->work_free.push_back(static_cast<int>(stream->d_work - ctx->d_work_pool));
+  stream->d_work = nullptr;
+}
+}  // namespace
 struct it_event {
   cudaEvent_t e = nullptr;
 };
@@ -284,11 +314,12 @@ it_status launch_bwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, 
 // tiles (long sequences: the tensor core never waits for a softmax), or two query tiles per CTA sharing
 // each K/V tile (short sequences: half as many CTA start-ups per unit of work).
 template <int D, bool PP>
-it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
+it_status launch_fwd_sm100(it_ctx* ctx, it_stream* stream, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, void* o, float* lse, const it::TensorStrides& stv,
                            const it::TensorStrides& skv, const it::TensorStrides& sq) {
   const int BH = B * H;
   const int Hkv = H / skv.group;
+  cudaStream_t s = stream->s;
   using T = std::conditional_t<PP, it::FwdPPTraits<D>, it::FwdTraits<D>>;
   auto kernel = PP ? it::fa_fwd_pp_sm100_kernel<D> : it::fa_fwd_sm100_kernel<D>;
   CUtensorMap mq, mk, mv;
@@ -311,13 +342,28 @@ it_status launch_fwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
   p.kv_group = skv.group;
+  // slices whose K and V (a third of L2 at most) are walked together by the two-query-tile kernel's work-item order
+  p.group_slices = static_cast<int>(std::clamp<long long>((40LL << 20) / (4LL * S * D), 1, BH));
   p.dec_tiles_per_split = 0;
   p.dec_n_splits = 1;
   p.dec_part_o = nullptr;
   p.dec_part_ml = nullptr;
   const int n_ctas_per_slice = (S + T::BM * T::QT_PER_CTA - 1) / (T::BM * T::QT_PER_CTA);
+  long long grid = static_cast<long long>(n_ctas_per_slice) * BH;
+  p.work_counter = nullptr;
+  if (!PP && grid > ctx->sm_count) {
+    // One CTA per SM; each draws its next work item from a counter (one per stream: launches on a stream run one
+    // after the other), zeroed in front of the launch.  IT_FWD_ONE_ITEM_PER_CTA=1 launches one CTA per item instead.
+    const char* one = getenv("IT_FWD_ONE_ITEM_PER_CTA");
+    if (stream->d_work != nullptr && (one == nullptr || one[0] != '1')) {
+      IT_CUDA(cudaMemsetAsync(stream->d_work, 0, sizeof(int), s));
+      stream->work_used = true;
+      p.work_counter = stream->d_work;
+      grid = ctx->sm_count;
+    }
+  }
   if (ctx->timing >= 2) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
-  kernel<<<static_cast<unsigned>(n_ctas_per_slice) * BH, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  kernel<<<static_cast<unsigned>(grid), T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
   if (ctx->timing >= 2) {
     IT_CUDA(cudaEventRecord(ctx->ev[0][1], s));
     ctx->ev_valid[0] = true;
@@ -567,6 +613,8 @@ it_status launch_decode_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv
   p.causal = 0;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
   p.kv_group = G;
+  p.group_slices = 1;
+  p.work_counter = nullptr;
   p.dec_tiles_per_split = tiles_per_split;
   p.dec_n_splits = n_splits;
   p.dec_part_o = ws;
@@ -657,6 +705,7 @@ it_status it_ctx_create(int device, it_ctx** out) {
   }
   c->encode = reinterpret_cast<EncodeTiledFn>(fn);
   if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess || cudaMemset(c->d_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaMalloc(&c->d_work_pool, it_ctx::WORK_SLOTS * sizeof(int)) != cudaSuccess ||
       cudaMallocHost(&c->h_status, sizeof(int)) != cudaSuccess ||
       cudaStreamCreateWithFlags(&c->status_stream, cudaStreamNonBlocking) != cudaSuccess) {
     delete c;
@@ -670,6 +719,7 @@ it_status it_ctx_destroy(it_ctx* ctx) {
   if (ctx == nullptr) return IT_OK;
   cudaSetDevice(ctx->device);
   cudaFree(ctx->d_status);
+  cudaFree(ctx->d_work_pool);
   cudaFreeHost(ctx->h_status);
   if (ctx->status_stream != nullptr) cudaStreamDestroy(ctx->status_stream);
   for (int a = 0; a < 4; ++a)
@@ -690,6 +740,7 @@ it_status it_stream_create(it_ctx* ctx, it_stream** out) {
     return fail(IT_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
   }
   s->owned = true;
+  s->d_work = take_work_slot(ctx);
   *out = s;
   return IT_OK;
 }
@@ -700,6 +751,7 @@ it_status it_stream_wrap(it_ctx* ctx, void* cuda_stream, it_stream** out) {
   if (s == nullptr) return fail(IT_ERR_CUDA, "out of host memory");
   s->s = static_cast<cudaStream_t>(cuda_stream);
   s->owned = false;
+  s->d_work = take_work_slot(ctx);
   *out = s;
   return IT_OK;
 }
@@ -707,6 +759,7 @@ it_status it_stream_wrap(it_ctx* ctx, void* cuda_stream, it_stream** out) {
 it_status it_stream_destroy(it_ctx* ctx, it_stream* stream) {
   if (stream == nullptr) return IT_OK;
   if (ctx != nullptr) cudaSetDevice(ctx->device);
+  give_work_slot(ctx, stream);
   if (stream->owned) cudaStreamDestroy(stream->s);
   delete stream;
   return IT_OK;
@@ -854,10 +907,10 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
     // for D = 64 at every length.
     const bool pp = (D == 128) && (S >= 4096);
     if (D == 128)
-      return pp ? launch_fwd_sm100<128, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
-                : launch_fwd_sm100<128, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
-    return pp ? launch_fwd_sm100<64, true>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
-              : launch_fwd_sm100<64, false>(ctx, stream->s, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
+      return pp ? launch_fwd_sm100<128, true>(ctx, stream, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
+                : launch_fwd_sm100<128, false>(ctx, stream, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
+    return pp ? launch_fwd_sm100<64, true>(ctx, stream, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
+              : launch_fwd_sm100<64, false>(ctx, stream, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);
   }
   return dtype == IT_F32 ? launch_fwd_generic<float>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv)
                          : launch_fwd_generic<__nv_bfloat16>(ctx, stream->s, BH, S, D, causal != 0, q, k, v, o, lse, sv, skv);
@@ -1248,6 +1301,7 @@ it_status it_host_step_destroy(it_host_step* hs) {
   for (int i = 0; i < it_host_step::MAX_STREAMS; ++i) {
     if (hs->streams[i].s != nullptr) {
       cudaStreamSynchronize(hs->streams[i].s);
+      give_work_slot(hs->ctx, &hs->streams[i]);
       cudaStreamDestroy(hs->streams[i].s);
     }
     if (hs->done[i] != nullptr) cudaEventDestroy(hs->done[i]);
@@ -1285,6 +1339,7 @@ it_status it_host_step_create(it_ctx* ctx, it_dtype dtype, int32_t group_slices,
   cudaError_t e = cudaEventCreateWithFlags(&hs->start, cudaEventDisableTiming);
   for (int i = 0; i < n_streams && e == cudaSuccess; ++i) {
     e = cudaStreamCreateWithFlags(&hs->streams[i].s, cudaStreamNonBlocking);
+    if (e == cudaSuccess) hs->streams[i].d_work = take_work_slot(ctx);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs->done[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&hs->dev[i]), per_stream);
   }
