@@ -52,7 +52,14 @@ it_status it_ctx_destroy(it_ctx* ctx);
 /* Text of the calling thread's last error (never null). */
 const char* it_last_error(void);
 
-/* CommandBatch::begin (src/command_batch.rs:174-182): a new in-order queue. */
+/* CommandBatch::begin (src/command_batch.rs:174-182): a new in-order queue.
+ * Every stream object (created or wrapped) holds one 4-byte work-item counter out of a pool of 4096 that the
+ * context allocates once: the bf16 forward for head_dim 64 and for head_dim 128 below 5120 keys starts one CTA
+ * per SM when it has more work items than SMs, zeroes the counter in front of the launch and lets the CTAs draw
+ * their next items from it.  Launches through one stream object run one after the other, so one counter is
+ * enough; a stream object created when the pool is empty gets none and its forwards start one CTA per item
+ * (same results).  A forward captured into a CUDA graph keeps the counter of the stream object it was captured
+ * through: do not run that graph beside other forwards of the same stream object on another stream. */
 it_status it_stream_create(it_ctx* ctx, it_stream** out);
 /* Adopts an existing cudaStream_t (0 = the legacy default stream) without owning it. */
 it_status it_stream_wrap(it_ctx* ctx, void* cuda_stream, it_stream** out);

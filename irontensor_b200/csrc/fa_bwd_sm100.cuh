@@ -349,6 +349,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // the dQ drain warpgroup (warps 12-15) hold a whole 128 x D fp32 tile in registers, so that tile
   // leaves TMEM in one go.  128*96 + 256*128 + 128*160 = 65536 <= 65536.
   const bool run = !bad_start && n_iter > 0;
+  static_assert(128 * 96 + 256 * 128 + 128 * 160 <= 512 * 128, "setmaxnreg budget exceeds the registers the CTA is launched with");
   if (warp < 4) {
     setmaxnreg_dec<96>();
     if (!run) {

@@ -4,7 +4,7 @@
 // Replaces, for bf16 tensors, the reference project's forward kernels
 // (src/shaders/flash_attention.metal:45-163 online softmax; :167-223 exact softmax) and adds the
 // per-row log-sum-exp output the fused backward needs.  The launcher picks this kernel for head_dim 128
-// and 4096 keys or more; fa_fwd_sm100.cuh (two query tiles per CTA) covers the rest.
+// and 5120 keys or more; fa_fwd_sm100.cuh (two query tiles per CTA) covers the rest.
 //
 // One CTA owns one 128-row query tile of one (batch, head) slice and walks its key tiles once:
 //   warp 0      : TMA producer  - the Q tile once, then a ring of K tiles (128-byte swizzle)
@@ -165,6 +165,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
   // Register budget: the control warpgroup keeps 80 per thread, the two softmax warpgroups take
   // 208 each so that a whole 128-column row of S stays in registers (128*80 + 256*208 = 63488).
+  static_assert(128 * 80 + 256 * 208 <= 384 * 168, "setmaxnreg budget exceeds the registers the CTA is launched with");
   if (warp < 4) {
     setmaxnreg_dec<80>();
     if (bad_start) {

@@ -1,6 +1,6 @@
 // Causal / full scaled-dot-product attention forward for bf16 inputs on sm_100a: two query tiles per
-// CTA sharing each K/V tile.  The launcher uses it for head_dim 64 and for sequences below 4096 keys
-// (half as many CTA start-ups per unit of work as fa_fwd_pp_sm100.cuh, which takes the long ones).
+// CTA sharing each K/V tile.  The launcher uses it for head_dim 64 and for sequences below 5120 keys
+// (fa_fwd_pp_sm100.cuh takes head_dim 128 from 5120 keys on).
 //
 // Replaces, for bf16 tensors with head_dim 64 or 128, the reference project's forward kernels
 // (src/shaders/flash_attention.metal:45-163 online softmax; :167-223 exact softmax) and adds the
@@ -205,10 +205,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   const bool bad_start = (*abort_flag != 0);
 
-  // Register budget: the control warpgroup keeps 80 per thread, the two softmax warpgroups take
-  // 208 each so that a whole 128-column row of S stays in registers (128*80 + 256*208 = 63488).
+  // Register budget: the control warpgroup keeps 88 per thread, the two softmax warpgroups take 208 each so that a
+  // whole 128-column row of S stays in registers.  The CTA owns what it was launched with, 384 threads x 168 registers;
+  // a request beyond that would leave setmaxnreg.inc waiting for registers that never come.
+  constexpr int REGS_CTRL = 88, REGS_SOFTMAX = 208;
+  static_assert(128 * REGS_CTRL + 256 * REGS_SOFTMAX <= 384 * 168, "setmaxnreg budget exceeds the CTA's registers");
   if (warp < 4) {
-    setmaxnreg_dec<80>();
+    setmaxnreg_dec<REGS_CTRL>();
     if (bad_start) {
       // nothing to do
     } else if (warp == 0) {
@@ -338,7 +341,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     }
   } else {
-    setmaxnreg_inc<208>();
+    setmaxnreg_inc<REGS_SOFTMAX>();
     // ------------------------------------------------------------ softmax + epilogue
     const int t = (warp - 4) >> 2;
     const int lane_base = (warp & 3) * 32;

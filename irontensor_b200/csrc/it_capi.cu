@@ -903,9 +903,11 @@ static it_status attention_fwd_impl(it_ctx* ctx, it_stream* stream, it_dtype dty
     sq.batch = skv.batch = qkv_row * S;
   }
   if (use_sm100_path(dtype, S, D)) {
-    // Crossover measured on B200 (causal): equal at S = 4096, D = 128; the two-tile kernel wins below and
-    // for D = 64 at every length.
-    const bool pp = (D == 128) && (S >= 4096);
+    // Crossover measured on B200 (causal, head_dim 128): the two-tile kernel wins by 3 % at S = 4096, the one-tile kernel by
+    // 1.5 % at 6144 and 6-10 % from 8192 on; the two-tile kernel takes head_dim 64 at every length.
+    // IT_FWD_KERNEL=pp|two in the environment overrides the choice (A/B runs).
+    const char* force = getenv("IT_FWD_KERNEL");
+    const bool pp = (force != nullptr) ? (force[0] == 'p') : ((D == 128) && (S >= 5120));
     if (D == 128)
       return pp ? launch_fwd_sm100<128, true>(ctx, stream, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq)
                 : launch_fwd_sm100<128, false>(ctx, stream, B, H, S, causal != 0, q, k, v, o, lse, sv, skv, sq);

@@ -556,15 +556,40 @@ def test_attention_with_another_key_length(it_ctx, B, Sq, Skv, H, D, bf16):
 
 @pytest.mark.parametrize("S,causal,qk_scale", [(4096, True, 1.0), (4100, True, 1.0), (4225, False, 1.0), (4352, True, 3.0),
                                                (4480, False, 3.0)])
-def test_bf16_long_sequence_forward(it_ctx, S, causal, qk_scale):
-    """The forward kernel for long sequences (head_dim 128, 4096 keys or more: one query tile per CTA, the two
-    softmax groups alternating over key tiles) against the oracle: ragged lengths, odd and even tile counts, no
-    mask, and scores spread widely enough that the reference maximum is raised (O rescaled) many times."""
+def test_bf16_long_sequence_forward(it_ctx, S, causal, qk_scale, monkeypatch):
+    """Both bf16 forward kernels at head_dim 128 on long sequences (the launcher picks by length; IT_FWD_KERNEL forces one):
+    one query tile per CTA with the two softmax groups alternating over key tiles, and two query tiles per work item
+    with one CTA per SM walking the items.  Against the oracle: ragged lengths, odd and even tile counts, no mask, and
+    scores spread widely enough that the reference maximum is raised (O rescaled) many times."""
     q, k, v, _ = seeded(90 + S, 1, 2, S, 128, bf16=True, qk_scale=qk_scale)
-    o, lse = gu.run_fwd(it_ctx, q, k, v, causal, bf16=True)
     ro, rlse = ol.fwd(q, k, v, causal)
-    assert np.abs(lse - rlse).max() <= 1e-4 * max(1.0, qk_scale ** 2)
-    check_bf16(o, ro, f"S={S} causal={causal} O")
+    for kernel in ("pp", "two"):
+        monkeypatch.setenv("IT_FWD_KERNEL", kernel)
+        o, lse = gu.run_fwd(it_ctx, q, k, v, causal, bf16=True)
+        assert np.abs(lse - rlse).max() <= 1e-4 * max(1.0, qk_scale ** 2), kernel
+        check_bf16(o, ro, f"S={S} causal={causal} {kernel} O")
+
+
+@pytest.mark.parametrize("B,H,S,D,causal", [(8, 12, 1024, 64, True), (5, 8, 1000, 64, True), (6, 10, 640, 128, True),
+                                            (40, 4, 256, 64, False), (3, 7, 2176, 64, True)])
+def test_forward_walking_work_items_matches_one_item_per_cta(it_ctx, B, H, S, D, causal, monkeypatch):
+    """More work items than SMs: the two-query-tile forward starts one CTA per SM and each walks items drawn from
+    the stream's counter.  An item's arithmetic does not depend on who runs it or after what, so O and LSE must
+    equal, bit for bit, what one CTA per item produces (IT_FWD_ONE_ITEM_PER_CTA=1); repeated launches on the same
+    stream re-zero the counter; a few slices are checked against the oracle as well."""
+    import torch
+    q, k, v, _ = seeded(700 + S + D, B, H, S, D, bf16=True)
+    monkeypatch.setenv("IT_FWD_KERNEL", "two")
+    monkeypatch.setenv("IT_FWD_ONE_ITEM_PER_CTA", "1")
+    o1, lse1 = gu.run_fwd(it_ctx, q, k, v, causal, bf16=True)
+    monkeypatch.delenv("IT_FWD_ONE_ITEM_PER_CTA")
+    for _ in range(3):
+        o2, lse2 = gu.run_fwd(it_ctx, q, k, v, causal, bf16=True)
+        assert np.array_equal(o1, o2) and np.array_equal(lse1, lse2)
+    for b, h in ((0, 0), (B - 1, H - 1), (B // 2, H // 3)):
+        ro, rlse = ol.fwd(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], causal)
+        assert np.abs(lse2[b:b + 1, h:h + 1] - rlse).max() <= 1e-4
+        check_bf16(o2[b:b + 1, h:h + 1], ro, f"slice ({b},{h}) O")
 
 
 @pytest.mark.parametrize("shape,bf16,causal", [
