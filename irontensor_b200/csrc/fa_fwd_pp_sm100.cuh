@@ -153,6 +153,22 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     fence_mbar_init();
     fence_proxy_async_smem();
   }
+  // The query tile and the first K and V tiles go out before the CTA-wide set-up (tensor-memory allocation, barrier,
+  // register hand-over), so their round trip to memory runs under it.  Nothing is loaded into a CTA that will not run.
+  if (threadIdx.x == 0 && *abort_flag == 0 && nkv > 0) {
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+    mbar_arrive_expect_tx(q_full, T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_Q + b * T::BLOCK_BYTES, &tmap_q, q_full, b * 64, qt * T::BM, hd, bt);
+    mbar_arrive_expect_tx(&k_full[0], T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_K + b * T::BLOCK_BYTES, &tmap_k, &k_full[0], b * 64, j0 * T::BN, hkv, bt);
+    mbar_arrive_expect_tx(&v_full[0], T::TILE_BYTES);
+    for (int b = 0; b < T::NBLK; ++b)
+      tma_load_4d(smem + T::SMEM_V + b * T::BLOCK_BYTES, &tmap_v, &v_full[0], b * 64, j0 * T::BN, hkv, bt);
+  }
   if (warp == 2) {
     tmem_alloc(tmem_slot, T::TMEM_COLS);
     tmem_relinquish();
@@ -172,14 +188,9 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // nothing to do
     } else if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
+      // (the query tile and K tile 0 were issued by this thread before the set-up barrier)
       if (lane == 0) {
-        prefetch_tensormap(&tmap_q);
-        prefetch_tensormap(&tmap_k);
-        prefetch_tensormap(&tmap_v);
-        mbar_arrive_expect_tx(q_full, T::TILE_BYTES);
-        for (int b = 0; b < T::NBLK; ++b)
-          tma_load_4d(smem + T::SMEM_Q + b * T::BLOCK_BYTES, &tmap_q, q_full, b * 64, qt * T::BM, hd, bt);
-        for (int i = 0; i < nkv; ++i) {
+        for (int i = 1; i < nkv; ++i) {
           const int st = i % T::STAGES;
           const uint32_t ph = (i / T::STAGES) & 1;
           if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
@@ -193,8 +204,9 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // ------------------------------------------------------------ TMA producer for V: a ring of its own,
       // because K runs two tiles ahead of V (S(j+2) is issued while P(j) is still being computed) and a
       // wait for a free V stage must not hold back the next K tile.
+      // (V tile 0 was issued by thread 0 before the set-up barrier)
       if (lane == 0) {
-        for (int i = 0; i < nkv; ++i) {
+        for (int i = 1; i < nkv; ++i) {
           const int st = i % T::STAGES;
           const uint32_t ph = (i / T::STAGES) & 1;
           if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;

@@ -486,6 +486,35 @@ def test_host_step_overlapped_chunks_match_device_resident(it_ctx):
     assert it_ctx.poll_status() == 0
 
 
+def test_forward_on_a_stream_object_without_a_work_counter(it_ctx):
+    """The context hands each stream object one work-item counter out of a pool of 4096.  A stream object wrapped when
+    the pool is empty has none: its forwards start one CTA per work item and give the same bits; destroying stream
+    objects hands their counters back."""
+    import torch
+    B, H, S, D = 6, 8, 1024, 64                      # 192 slices x 4 pairs of query tiles: more items than SMs
+    q, k, v, _ = seeded(811, B, H, S, D, bf16=True)
+    tq, tk, tv = (gu.to_dev(x, True) for x in (q, k, v))
+    ref_o, ref_lse = torch.empty_like(tq), torch.empty((B, H, S), device="cuda")
+    raw.fwd(_lib.IT_BF16, B, H, S, D, True, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), ref_o.data_ptr(), ref_lse.data_ptr(), ctx=it_ctx)
+    lib, cur = it_ctx.lib, torch.cuda.current_stream().cuda_stream
+    wrapped = []
+    try:
+        for _ in range(4200):
+            h = ctypes.c_void_p()
+            _lib.check(lib.it_stream_wrap(it_ctx.handle, ctypes.c_void_p(cur), ctypes.byref(h)))
+            wrapped.append(h)
+        for h in (wrapped[0], wrapped[-1]):          # one with a counter, one without
+            o, lse = torch.full_like(tq, float("nan")), torch.full((B, H, S), float("nan"), device="cuda")
+            _lib.check(lib.it_flash_attention_fwd(it_ctx.handle, h, _lib.IT_BF16, B, H, S, D, 1, tq.data_ptr(), tk.data_ptr(),
+                                                  tv.data_ptr(), o.data_ptr(), lse.data_ptr()))
+            torch.cuda.synchronize()
+            assert torch.equal(o, ref_o) and torch.equal(lse, ref_lse)
+    finally:
+        for h in wrapped:
+            lib.it_stream_destroy(it_ctx.handle, h)
+    assert it_ctx.poll_status() == 0
+
+
 def test_kernel_timers_and_profiler_tags(it_ctx):
     """The device-side timers that stand in for the reference's profiler categories (OpCategory::FlashAttention,
     src/ops/flash_attention.rs:77; attn_bwd/* in src/train/helpers.rs:126-183): levels 1 to 3 bracket more kernels."""
