@@ -126,6 +126,11 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   };
   // The n-th item of this CTA, as the roles other than the scheduler see it: 1 = there is one, 0 = no more, -1 = gave up.
   auto fetch = [&](uint32_t n, Item& it) -> int {
+    if (prm.work_counter == nullptr) {   // one item per CTA (a launch no larger than the GPU): nothing to wait for
+      if (n > 0) return 0;
+      decode(static_cast<int>(blockIdx.x), it);
+      return 1;
+    }
     if (!mbar_wait(&sched_full[n & 1], (n >> 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) return -1;
     const int idx = sched_item[n & 1];
     if (idx < 0) return 0;
@@ -323,14 +328,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     } else if (warp == 3) {
       // ------------------------------------------------------------ work-item scheduler (one thread)
-      if (lane == 0) {
+      if (lane == 0 && prm.work_counter != nullptr) {
         for (uint32_t n = 0;; ++n) {
           // the slot's previous item (n - 2) has been released by every role
           if (n >= 2 && !mbar_wait(&sched_empty[n & 1], ((n >> 1) - 1) & 1, abort_flag, prm.status, DEV_ERR_TIMEOUT_EMPTY)) break;
-          int idx = -1;
-          if (n == 0) {
-            idx = static_cast<int>(blockIdx.x);
-          } else if (prm.work_counter != nullptr) {
+          int idx = static_cast<int>(blockIdx.x);
+          if (n > 0) {
             idx = G + atomicAdd(prm.work_counter, 1);
             if (idx >= n_items) idx = -1;
           }
