@@ -55,7 +55,7 @@ struct FwdParams {
   int causal;
   float scale_log2;     // 1/sqrt(D) * log2(e)
   int kv_group;         // query heads per K/V head (grouped-query attention; 1 otherwise)
-  int group_slices;     // fa_fwd_sm100_kernel: slices per group of its work-item order (their K and V fit in L2)
+  int group_slices;     // fa_fwd_sm100_kernel: slices per group of its work-item order
   int* work_counter;    // fa_fwd_sm100_kernel: zeroed before the launch when the grid is smaller than the number of work items, else null
   // decode instantiation of the long-sequence kernel only (one new token against a key/value cache):
   int dec_tiles_per_split;   // key tiles per CTA
@@ -98,7 +98,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // current item's last tiles are in the softmax, and the MMA thread issues the next item's first S tiles right
   // behind the current item's last P V, so that a CTA pays set-up, first-load latency and tear-down once and not
   // once per item (at a thousand keys an item is a handful of tiles long and they were a quarter of its life).
-  // Item order: slices in groups whose K and V fit in L2 together; within a group the pairs with the most key
+  // Item order: slices in groups chosen by the launcher (a bound on the K and V bytes in work at once); within a group the pairs with the most key
   // tiles first, all slices of the group for one pair, then the next pair.  A CTA's first item is its own index;
   // the following ones it draws from a counter in global memory (warp 3), one item ahead of the softmax groups, and
   // hands to the other roles through a two-slot ring in shared memory: the lightest items come last, so the CTAs

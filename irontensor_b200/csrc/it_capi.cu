@@ -342,8 +342,14 @@ it_status launch_fwd_sm100(it_ctx* ctx, it_stream* stream, int B, int H, int S, 
   p.causal = causal;
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
   p.kv_group = skv.group;
-  // slices whose K and V (a third of L2 at most) are walked together by the two-query-tile kernel's work-item order
-  p.group_slices = static_cast<int>(std::clamp<long long>((40LL << 20) / (4LL * S * D), 1, BH));
+  // Slices whose work items the two-query-tile kernel hands out together (heaviest pairs of all of them first): as many
+  // as have 40 MB of K and V at head_dim 128, 96 MB at head_dim 64.  Measured on B200 (causal): at head_dim 128 larger
+  // groups lose up to 12 % once K and V of the whole launch exceed L2 (B32 H16 S4096: 2.15 ms at 40 MB, 2.41 ms ungrouped);
+  // at head_dim 64, where a tile is half as many bytes, 96 MB gains 5-8 % at 2048 and 8192 keys (B4 H16 S8192: 0.916 ->
+  // 0.854 ms) and is within noise elsewhere.  IT_FWD_GROUP_MB in the environment overrides it (A/B runs).
+  long long group_mb = (D == 64) ? 96 : 40;
+  if (const char* e = getenv("IT_FWD_GROUP_MB")) group_mb = std::max(1, atoi(e));
+  p.group_slices = static_cast<int>(std::clamp<long long>((group_mb << 20) / (4LL * S * D), 1, BH));
   p.dec_tiles_per_split = 0;
   p.dec_n_splits = 1;
   p.dec_part_o = nullptr;
