@@ -343,13 +343,20 @@ it_status launch_fwd_sm100(it_ctx* ctx, it_stream* stream, int B, int H, int S, 
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * 1.4426950408889634f;
   p.kv_group = skv.group;
   // Slices whose work items the two-query-tile kernel hands out together (heaviest pairs of all of them first): as many
-  // as have 40 MB of K and V at head_dim 128, 96 MB at head_dim 64.  Measured on B200 (causal): at head_dim 128 larger
-  // groups lose up to 12 % once K and V of the whole launch exceed L2 (B32 H16 S4096: 2.15 ms at 40 MB, 2.41 ms ungrouped);
-  // at head_dim 64, where a tile is half as many bytes, 96 MB gains 5-8 % at 2048 and 8192 keys (B4 H16 S8192: 0.916 ->
-  // 0.854 ms) and is within noise elsewhere.  IT_FWD_GROUP_MB in the environment overrides it (A/B runs).
+  // as have 40 MB of K and V at head_dim 128, 96 MB at head_dim 64, in groups of equal size.  Measured on B200 (causal): at
+  // head_dim 128 larger groups lose once K and V of the whole launch exceed L2 (B32 H16 S4096: 2.12 ms at 40 MB, 2.18 at
+  // 96 MB, 2.41 ungrouped; B64 H16 S1024: 0.39 / 0.43 / 0.48 ms); at head_dim 64, where a tile is half as many bytes, 96 MB
+  // is about 1 % ahead.  Equal groups matter more than the size: with 64 slices in groups of 20, 20, 20, 4 the last group's
+  // heaviest items ran at the very end with few CTAs left to share them (B4 H16 S8192 D64: 0.916 ms, 0.850 in four groups
+  // of 16).  IT_FWD_GROUP_MB in the environment overrides the size (A/B runs).
   long long group_mb = (D == 64) ? 96 : 40;
   if (const char* e = getenv("IT_FWD_GROUP_MB")) group_mb = std::max(1, atoi(e));
-  p.group_slices = static_cast<int>(std::clamp<long long>((group_mb << 20) / (4LL * S * D), 1, BH));
+  {
+    // equal groups: a short last group would put its heaviest items at the very end of the launch, with few CTAs left to share them
+    const long long gs_max = std::clamp<long long>((group_mb << 20) / (4LL * S * D), 1, BH);
+    const long long n_groups = (BH + gs_max - 1) / gs_max;
+    p.group_slices = static_cast<int>((BH + n_groups - 1) / n_groups);
+  }
   p.dec_tiles_per_split = 0;
   p.dec_n_splits = 1;
   p.dec_part_o = nullptr;
