@@ -621,7 +621,7 @@ def secondary_configs(ctx, peaks):
         out[name] = r
 
     def c1():
-        m = measure_c1(ctx, peaks, flush, 200, 3)
+        m = measure_c1(ctx, peaks, flush, 600, 3)   # long enough for a few clock samples to land inside
         return {"workload": m["config"]["workload"], "us": m["value"], "us_warm_l2": m["us_warm_l2"], "gbs": m["gbs"],
                 "frac_of_hbm_peak": m["roofline"]["frac"], "tflops": m["tflops"]}
 
