@@ -94,6 +94,8 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
   constexpr int EL = D / 16;       // elements per lane and row: 8 (D = 128) or 4 (D = 64)
   const int lane = threadIdx.x & 31;
   const int sub = lane & 15, half = lane >> 4;
+  ptx::grid_dep_wait();     // O and LSE come from the kernel in front (the forward); the accumulator it clears may still be read
+  ptx::grid_dep_launch();   // the main kernel may set itself up meanwhile; it waits for this pass before its first load
   const long long row0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * RW;
   if (row0 >= static_cast<long long>(BH) * S_pad) return;
   const int bh = static_cast<int>(row0 / S_pad);
@@ -171,6 +173,7 @@ __global__ void fa_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const
 __global__ void fa_bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq,
                                      size_t n_vec4, float scale, int S, int D, ptx::TensorStrides st,
                                      const __grid_constant__ RopeFreqs freqs) {
+  ptx::grid_dep_wait();   // every reduce-add of the main kernel has landed
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_vec4) return;
   float4 v = reinterpret_cast<const float4*>(dq_accum)[i];
@@ -322,6 +325,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // their round trip to memory runs under it: a short-sequence CTA lives for a handful of tiles and this wait is a
   // visible part of its life.  Nothing is loaded into a CTA that is not going to run.
   if (threadIdx.x == 0 && *abort_flag == 0 && n_iter > 0) {
+    grid_dep_wait();   // LSE*log2e, delta and the cleared dQ accumulator come from the prepare pass in front
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
@@ -342,6 +346,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dep_wait();     // (thread 0 has been through it; the others write to memory the prepare pass wrote as well)
+  grid_dep_launch();   // the finish pass may be set up; it waits for this kernel to complete before it reads
   const uint32_t tmem_base = *tmem_slot;
   const bool bad_start = (*abort_flag != 0);
 

@@ -176,6 +176,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dep_launch();   // a dependent launch behind this kernel (the backward's prepare pass) may be set up meanwhile
   const uint32_t tmem_base = *tmem_slot;
   const bool bad_start = (*abort_flag != 0) || nkv <= 0;   // an empty split (the launcher makes none) must not wait
 

@@ -408,6 +408,23 @@ BwdWorkspace bwd_workspace_layout(it_dtype dtype, int64_t BH, int64_t S, int64_t
   return w;
 }
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may be set up while the kernel in front of it
+// in the stream still runs, and waits in griddepcontrol.wait for that kernel's completion before it touches its results.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
 template <int D>
 it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int causal, const void* q, const void* k,
                            const void* v, const void* o, const void* d_o, const float* lse, void* dq, void* dk,
@@ -449,9 +466,9 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   const size_t n_dq = static_cast<size_t>(BH) * S * D;
   const long long rows_pad = static_cast<long long>(BH) * w.S_pad;
   if (ctx->timing >= 3) IT_CUDA(cudaEventRecord(ctx->ev[2][0], s));
-  it::fa_bwd_prepare_kernel<D><<<static_cast<unsigned>((rows_pad / 8 + 7) / 8), 256, 0, s>>>(   // 8 rows per warp, 8 warps
-      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, dq_accum, S,
-      w.S_pad, BH, stv);
+  IT_CUDA(launch_dependent(it::fa_bwd_prepare_kernel<D>, static_cast<unsigned>((rows_pad / 8 + 7) / 8), 256, 0, s,   // 8 rows per warp, 8 warps
+                           static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2, delta, dq_accum, S,
+                           w.S_pad, BH, stv));
   it::BwdParams p;
   p.st = stv;
   p.st_kv = skv;
@@ -482,19 +499,20 @@ it_status launch_bwd_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int S, int
   if (ctx->timing) IT_CUDA(cudaEventRecord(ctx->ev[1][0], s));
   if constexpr (D == 64) {
     if (two_tiles)
-      it::fa_bwd_sm100_kernel<D, 2><<<static_cast<unsigned>((n_kt + 1) / 2) * B * Hkv, T::THREADS, it::BwdTraits<D, 2>::SMEM_BYTES, s>>>(
-          mq, mk, mv, mdo, mdq, p, rf);
+      IT_CUDA(launch_dependent(it::fa_bwd_sm100_kernel<D, 2>, static_cast<unsigned>((n_kt + 1) / 2) * B * Hkv, T::THREADS,
+                               it::BwdTraits<D, 2>::SMEM_BYTES, s, mq, mk, mv, mdo, mdq, p, rf));
   }
   if (!two_tiles)
-    it::fa_bwd_sm100_kernel<D, 1><<<static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, mdo, mdq, p, rf);
+    IT_CUDA(launch_dependent(it::fa_bwd_sm100_kernel<D, 1>, static_cast<unsigned>(n_kt) * B * Hkv, T::THREADS, T::SMEM_BYTES, s,
+                             mq, mk, mv, mdo, mdq, p, rf));
   if (ctx->timing) {
     IT_CUDA(cudaEventRecord(ctx->ev[1][1], s));
     ctx->ev_valid[1] = true;
   }
   if (ctx->timing >= 3) IT_CUDA(cudaEventRecord(ctx->ev[3][0], s));
   const size_t n4 = n_dq / 4;
-  it::fa_bwd_finish_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, s>>>(
-      dq_accum, static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, sq, rf);
+  IT_CUDA(launch_dependent(it::fa_bwd_finish_kernel, static_cast<unsigned>((n4 + 255) / 256), 256, 0, s,
+                           static_cast<const float*>(dq_accum), static_cast<__nv_bfloat16*>(dq), n4, p.scale, S, D, sq, rf));
   if (ctx->timing >= 3) {
     IT_CUDA(cudaEventRecord(ctx->ev[3][1], s));
     ctx->ev_valid[3] = true;

@@ -126,6 +126,13 @@ __device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity,
   return true;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel in front of it in the stream still runs: grid_dep_wait() is where it waits for that kernel to have
+// completed and its writes to be visible (a no-op in a kernel launched without the attribute); grid_dep_launch() in the
+// kernel in front allows the dependent to be started once every CTA has executed it or exited.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMA (tiled, CTA-local, no multicast)
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
