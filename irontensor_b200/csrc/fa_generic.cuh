@@ -173,6 +173,10 @@ fa_fwd_rows_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
                        float* __restrict__ o, float* __restrict__ lse, int S, int Skv, int D, int causal, float scale_log2,
                        TensorStrides st, TensorStrides skv) {
   constexpr int TK = 32, NT = 32 * (RB / RW);   // RB rows per CTA: RB / RW warps, RW rows each
+  // Launched as a programmatic dependent: a chain of per-token calls (generation without a key/value cache) then pays
+  // each call's launch latency under the previous call's execution.  The inputs may be what the kernel in front wrote.
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
   extern __shared__ __align__(16) float sm[];
   const int DS = D + 4;                       // padded row stride (floats)
   float* sQ = sm;                             // [RB][D]

@@ -195,6 +195,23 @@ it_status check_common(it_ctx* ctx, it_stream* stream, it_dtype dtype, int32_t B
   return IT_OK;
 }
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may be set up while the kernel in front of it
+// in the stream still runs, and waits in griddepcontrol.wait for that kernel's completion before it touches its results.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
 // The tensor-core kernels take bf16 tensors with head_dim 64 or 128 and at least one full tile.
 bool use_sm100_path(it_dtype dtype, int32_t S, int32_t D) {
   return dtype == IT_BF16 && (D == 64 || D == 128) && S >= 128;
@@ -252,18 +269,18 @@ it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, 
     const int rw = (static_cast<long long>(g16.x) * g16.y <= ctx->sm_count) ? 2 : 4;
     const unsigned nt = 32u * (16u / static_cast<unsigned>(rw));
     if (D <= 32) {
-      if (rw == 2) it::fa_fwd_rows_f32_kernel<1, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
-      else it::fa_fwd_rows_f32_kernel<1, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      if (rw == 2) IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<1, 2>, g16, dim3(nt), smem, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
+      else IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<1, 4>, g16, dim3(nt), smem, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
     } else if (D <= 64 && static_cast<long long>(g16.x) * g16.y > 4LL * ctx->sm_count) {
       // Many CTAs per SM (the reference's TINY training shape, batch 16 x 4 heads x 256 keys): the kernel is
       // bound by its shared-memory loads, and 32-row CTAs with eight rows per warp use every K chunk and V
       // row for twice as many rows (49 against 53 us on that shape).
       const int smem32 = (32 * D + 4 * 32 * (D + 4) + 32 * 32) * 4;
       const dim3 g32((S + 31) / 32, BH);
-      it::fa_fwd_rows_f32_kernel<2, 8, 32><<<g32, 128, smem32, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<2, 8, 32>, g32, dim3(128), smem32, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
     } else if (D <= 64) {
-      if (rw == 2) it::fa_fwd_rows_f32_kernel<2, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
-      else it::fa_fwd_rows_f32_kernel<2, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      if (rw == 2) IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<2, 2>, g16, dim3(nt), smem, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
+      else IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<2, 4>, g16, dim3(nt), smem, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
     } else {
       static std::atomic<bool> attr_set[16];   // zero-initialised; setting an attribute twice is harmless
       if (!attr_set[ctx->device & 15]) {
@@ -273,8 +290,8 @@ it_status launch_fwd_generic(it_ctx* ctx, cudaStream_t s, int BH, int S, int D, 
                                      (16 * 128 + 4 * 32 * 132 + 512) * 4));
         attr_set[ctx->device & 15] = true;
       }
-      if (rw == 2) it::fa_fwd_rows_f32_kernel<4, 2><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
-      else it::fa_fwd_rows_f32_kernel<4, 4><<<g16, nt, smem, s>>>(qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv);
+      if (rw == 2) IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<4, 2>, g16, dim3(nt), smem, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
+      else IT_CUDA(launch_dependent(it::fa_fwd_rows_f32_kernel<4, 4>, g16, dim3(nt), smem, s, qf, kf, vf, of, lse, S, Skv, D, causal, scale, st, skv));
     }
     ctx->launches += 1;
     IT_CUDA(cudaGetLastError());
@@ -406,23 +423,6 @@ BwdWorkspace bwd_workspace_layout(it_dtype dtype, int64_t BH, int64_t S, int64_t
   }
   if (w.total == 0) w.total = 256;
   return w;
-}
-
-// Launch with the programmatic-stream-serialization attribute: the kernel may be set up while the kernel in front of it
-// in the stream still runs, and waits in griddepcontrol.wait for that kernel's completion before it touches its results.
-template <typename... KArgs, typename... Args>
-cudaError_t launch_dependent(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Args&&... args) {
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(block);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
 }
 
 template <int D>
