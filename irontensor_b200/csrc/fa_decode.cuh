@@ -222,6 +222,8 @@ fa_decode_split_kernel(const ST* __restrict__ q, const ST* __restrict__ k_cache,
 template <typename ST>
 __global__ void fa_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        ST* __restrict__ o, float* __restrict__ lse, int n_splits, int D) {
+  ptx::grid_dep_wait();     // the partial results come from the kernel in front
+  ptx::grid_dep_launch();
   const size_t bh = blockIdx.x;
   const int d = threadIdx.x;
   float m = -INFINITY;

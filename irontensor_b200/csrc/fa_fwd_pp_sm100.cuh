@@ -156,6 +156,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   // The query tile and the first K and V tiles go out before the CTA-wide set-up (tensor-memory allocation, barrier,
   // register hand-over), so their round trip to memory runs under it.  Nothing is loaded into a CTA that will not run.
   if (threadIdx.x == 0 && *abort_flag == 0 && nkv > 0) {
+    grid_dep_wait();   // the inputs may be what the kernel in front of this one wrote (no-op unless launched as its dependent)
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
@@ -176,6 +177,7 @@ fa_fwd_pp_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dep_wait();     // (thread 0 has been through it; the others write outputs the kernel in front may still read)
   grid_dep_launch();   // a dependent launch behind this kernel (the backward's prepare pass) may be set up meanwhile
   const uint32_t tmem_base = *tmem_slot;
   const bool bad_start = (*abort_flag != 0) || nkv <= 0;   // an empty split (the launcher makes none) must not wait

@@ -393,7 +393,7 @@ it_status launch_fwd_sm100(it_ctx* ctx, it_stream* stream, int B, int H, int S, 
     }
   }
   if (ctx->timing >= 2) IT_CUDA(cudaEventRecord(ctx->ev[0][0], s));
-  kernel<<<static_cast<unsigned>(grid), T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  IT_CUDA(launch_dependent(kernel, static_cast<unsigned>(grid), T::THREADS, T::SMEM_BYTES, s, mq, mk, mv, p));
   if (ctx->timing >= 2) {
     IT_CUDA(cudaEventRecord(ctx->ev[0][1], s));
     ctx->ev_valid[0] = true;
@@ -650,11 +650,12 @@ it_status launch_decode_sm100(it_ctx* ctx, cudaStream_t s, int B, int H, int Hkv
   p.dec_n_splits = n_splits;
   p.dec_part_o = ws;
   p.dec_part_ml = ws + static_cast<size_t>(B) * H * n_splits * D;
-  kernel<<<static_cast<unsigned>(base_ctas * n_splits), T::THREADS, T::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  IT_CUDA(launch_dependent(kernel, static_cast<unsigned>(base_ctas * n_splits), T::THREADS, T::SMEM_BYTES, s, mq, mk, mv, p));
   ctx->launches += 1;
   if (n_splits > 1) {
-    it::fa_decode_merge_kernel<__nv_bfloat16><<<B * H, 128, 0, s>>>(p.dec_part_o, p.dec_part_ml, static_cast<__nv_bfloat16*>(o),
-                                                                    lse, n_splits, D);
+    IT_CUDA(launch_dependent(it::fa_decode_merge_kernel<__nv_bfloat16>, static_cast<unsigned>(B * H), 128, 0, s,
+                             static_cast<const float*>(p.dec_part_o), static_cast<const float*>(p.dec_part_ml),
+                             static_cast<__nv_bfloat16*>(o), lse, n_splits, D));
     ctx->launches += 1;
   }
   IT_CUDA(cudaGetLastError());
